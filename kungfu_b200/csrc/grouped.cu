@@ -9,12 +9,14 @@
 //       are the (token, choice) pairs sorted by expert; `row_index` then names the source row of a sorted row
 //       (row_index[r] / row_div), or the sorted row itself when absent.
 //   gated = 1: w_g holds 2N rows (gate rows, then up rows) and out = act(gate, up) with the clamped form
-//       g = min(gate, limit), u = clamp(up, -limit, limit), out = g * sigmoid(1.702 g) * (u + 1).
+//       g = min(gate, limit), u = clamp(up, -limit, limit), out = g * sigmoid(1.702 g) * (u + 1);
+//   gated = 2: the same rows with out = gate * sigmoid(gate) * up.
 //
-// kf_moe_route: sigmoid scores, a correction added for the choice only, groups of neighbouring experts ranked by the sum
-//   of their two largest choice scores, the best `keep` groups stay eligible, the `top` largest eligible choice scores
-//   win (lower index first among equals); weights = the winners' uncorrected scores, divided by their sum + 1e-20,
-//   times `scale`.  One warp per token, everything 32-bit.
+// kf_moe_route: sigmoid scores (or, `softmax`, the softmax over all experts), a correction added for the choice only,
+//   groups of neighbouring experts ranked by the sum of their two largest choice scores (or, `group_best` = 1, by their
+//   largest), the best `keep` groups stay eligible, the `top` largest eligible choice scores win (lower index first
+//   among equals); weights = the winners' uncorrected scores, divided by their sum + 1e-20 when `normalize`, times
+//   `scale`.  One warp per token, everything 32-bit.
 // kf_moe_plan: counts the pairs of every expert, lays the pairs out expert by expert (sorted_pair, inverse), and lists
 //   the row tiles of every expert.  One block; the order inside an expert is whatever the atomics give, which no
 //   result depends on (a pair's output row is computed from its own row alone).
@@ -106,10 +108,7 @@ __global__ void __launch_bounds__(256) grouped_simt_kernel(KfGroupedArgs p) {
       const int c = col0 + tx * 4 + j;
       if (c >= N) continue;
       float v = acc[i][j];
-      if (GATED) {
-        const float gt = fminf(v, p.limit), up = fminf(fmaxf(acu[i][j], -p.limit), p.limit);
-        v = gt / (1.f + expf(-1.702f * gt)) * (up + 1.f);
-      }
+      if (GATED) v = p.gated == 2 ? v / (1.f + expf(-v)) * acu[i][j] : kf_clamped_swish(v, acu[i][j], p.limit);
       kf_store(out, (size_t)(r0 + r) * p.ldo + c, v);
     }
   }
@@ -229,7 +228,9 @@ __global__ void __launch_bounds__(256) grouped_mma_kernel(KfGroupedArgs p) {
         const int r = wm * 32 + mi * 16 + gid + (i >= 2 ? 8 : 0);
         const int c = col0 + (GATED ? wn * 16 + nt * 8 : wn * 32 + nt * 8) + 2 * tig + (i & 1);
         if (r >= nrows || c >= N) continue;
-        const float v = GATED ? kf_clamped_swish(acc[mi][nt][i], acc[mi][nt + 2][i], p.limit) : acc[mi][nt][i];
+        const float v = !GATED ? acc[mi][nt][i]
+                        : (p.gated == 2 ? acc[mi][nt][i] / (1.f + expf(-acc[mi][nt][i])) * acc[mi][nt + 2][i]
+                                        : kf_clamped_swish(acc[mi][nt][i], acc[mi][nt + 2][i], p.limit));
         kf_store(out, (size_t)(r0 + r) * p.ldo + c, v);
       }
 }
@@ -297,7 +298,8 @@ constexpr int KF_MOE_MAX_EXPERTS = 1024;
 
 template <typename TW>
 __global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict__ logits, const TW* __restrict__ correction,
-                                                        int T, int E, int G, int keep, int top, float scale,
+                                                        int T, int E, int G, int keep, int top, float scale, int softmax,
+                                                        int group_best, int normalize,
                                                         int* __restrict__ ids, float* __restrict__ weights) {
   kf_pdl_trigger();
   kf_pdl_wait();
@@ -309,8 +311,16 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict_
   float* choice = score + E;                           // corrected; -inf when not eligible or already taken
   float* gscore = choice + E;
   const float NEG = -INFINITY;
+  float zmax = NEG, zsum = 0.f;
+  if (softmax) {
+    for (int e = lane; e < E; e += 32) zmax = fmaxf(zmax, logits[(size_t)t * E + e]);
+    zmax = kf_warp_max(zmax);
+    for (int e = lane; e < E; e += 32) zsum += expf(logits[(size_t)t * E + e] - zmax);
+    zsum = kf_warp_sum(zsum);
+  }
   for (int e = lane; e < E; e += 32) {
-    const float s = 1.f / (1.f + expf(-logits[(size_t)t * E + e]));
+    const float z = logits[(size_t)t * E + e];
+    const float s = softmax ? expf(z - zmax) / zsum : 1.f / (1.f + expf(-z));
     score[e] = s;
     const float c = s + (correction ? kf_load(correction, e) : 0.f);
     choice[e] = c == c ? c : NEG;                      // a row of padding may hold anything
@@ -324,7 +334,7 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict_
         const float c = choice[g * per + i];
         if (c > a) { b = a; a = c; } else if (c > b) b = c;
       }
-      gscore[g] = per > 1 ? a + b : a;
+      gscore[g] = (per > 1 && group_best != 1) ? a + b : a;
     }
     __syncwarp();
     // the best `keep` groups stay; mark them by +inf one after the other, then close the others
@@ -370,22 +380,22 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict_
   }
   for (int r = lane; r < top; r += 32) {
     const int e = ids[(size_t)t * top + r];
-    weights[(size_t)t * top + r] = score[e] / (sum + 1e-20f) * scale;
+    weights[(size_t)t * top + r] = (normalize ? score[e] / (sum + 1e-20f) : score[e]) * scale;
   }
 }
 
 KF_API int kf_moe_route(const float* logits, const void* correction, int w_dtype, int T, int E, int G, int keep, int top,
-                        float scale, int* ids, float* weights, cudaStream_t stream) {
+                        float scale, int softmax, int group_best, int normalize, int* ids, float* weights, cudaStream_t stream) {
   if (T <= 0) return KF_OK;
   if (E < 1 || E > KF_MOE_MAX_EXPERTS || top < 1 || top > E || G < 1 || E % G || keep < 1 || keep > G) return KF_ERR_SIZE;
   if (G > 1 && keep * (E / G) < top) return KF_ERR_SIZE;
   const size_t smem = (size_t)4 * (2 * E + G) * sizeof(float);
   const dim3 grid(kf_ceil_div(T, 4));
   if (w_dtype == KF_F32)
-    kf_launch(moe_route_kernel<float>, grid, dim3(128), smem, stream, logits, (const float*)correction, T, E, G, keep, top, scale, ids, weights);
+    kf_launch(moe_route_kernel<float>, grid, dim3(128), smem, stream, logits, (const float*)correction, T, E, G, keep, top, scale, softmax, group_best, normalize, ids, weights);
   else if (w_dtype == KF_BF16)
     kf_launch(moe_route_kernel<__nv_bfloat16>, grid, dim3(128), smem, stream, logits, (const __nv_bfloat16*)correction, T, E, G, keep,
-              top, scale, ids, weights);
+              top, scale, softmax, group_best, normalize, ids, weights);
   else return KF_ERR_DTYPE;
   KF_CHECK_LAUNCH();
   return KF_OK;

@@ -1,0 +1,185 @@
+// Attention whose softmax weights are mixed across heads after the softmax ("talking heads"), served by the ordinary
+// attention kernels.
+//
+// With H query heads, G key/value heads, r = H / G, and a mixing matrix M [H, H]:
+//   a_g(i, .) = softmax over the visible keys of head g's scores            (each head's own weights)
+//   b_h(i, j) = sum_g M[h, g] a_g(i, j)                                       (mixed weights)
+//   out_h(i)  = sum_j b_h(i, j) v_(h / r)(j)  =  sum_g M[h, g] * O[g, h / r](i),   O[g, c] = sum_j a_g(., j) v_c(j).
+// O[g, c] is plain attention of query head g over the keys of its own key head and the values of value head c, so the
+// attention kernels run H * G "wide" heads over G * G wide key/value heads: wide key/value head (ck, cv) holds the keys
+// of head ck and the values of head cv, and wide query head ((ck * G + cv) * r + i) is query head g = ck * r + i.
+//
+// kf_rotate_norm_append: from the 32-bit q|k|v projection to those operands.  Per head of q and k: the first `rot`
+//   elements are turned in pairs (i, i + rot/2) by the step's cos/sin table times `mag`, then (when `unit_norm`) the head
+//   is divided by sqrt(mean(head^2) + eps); v passes as it is.  q goes to its G wide query heads, k to the wide heads
+//   (ck, *), v to the wide heads (*, cv), at the token's place in the request's pages.  With wide = 0 nothing is
+//   repeated (G plain key/value heads).  Heads use D elements in q and pages, tails zero.
+// kf_head_mix_gate: out[t, h * dv + e] = gate(t, h * dv + e) * sum_g M[h, g] * o[t, wide(g, h / r), e], sums in 32-bit in
+//   ascending g, gate = sigmoid of a column range of a 32-bit matrix (null: no gate).  Without M (null) it is the gate
+//   and the packing alone.
+// One warp per (row, head); everything is computed in 32-bit, only the stores round.
+#include "common.cuh"
+
+constexpr int HM_MAX_D = 256;
+constexpr int HM_WARPS = 4;
+
+template <typename TQ, typename TKV>
+__global__ void __launch_bounds__(HM_WARPS * 32)
+rotate_norm_append_kernel(const float* __restrict__ in, int ld, int col0, const float* __restrict__ cos_t,
+                          const float* __restrict__ sin_t, int rot, float mag, int unit_norm, float eps, int nh, int nkv,
+                          int dk, int dv, int D, int wide, const int* __restrict__ positions,
+                          const int* __restrict__ row_req, const int* __restrict__ block_table, int table_stride,
+                          int page_size, TKV* __restrict__ pages, TQ* __restrict__ q_out, int write_kv, int T) {
+  kf_pdl_trigger();
+  kf_pdl_wait();
+  __shared__ float hs[HM_WARPS][HM_MAX_D];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int slots = nh + 2 * nkv;
+  const long item = (long)blockIdx.x * HM_WARPS + warp;
+  if (item >= (long)T * slots) return;                      // whole warps leave; only __syncwarp below
+  const int t = (int)(item / slots), hslot = (int)(item - (long)t * slots);
+  const int req = row_req[t];
+  const int kind = hslot < nh ? 0 : (hslot < nh + nkv ? 1 : 2);            // query, key, value
+  const int head = kind == 0 ? hslot : (kind == 1 ? hslot - nh : hslot - nh - nkv);
+  const int reps = wide ? nkv : 1;
+  const int per = nh / nkv;
+  const int nq = nh * reps, nst = nkv * reps;               // query heads and stored key/value heads as the attention sees them
+  if (req < 0) {                                            // padding row: zero queries, nothing filed
+    if (kind == 0)
+      for (int c = 0; c < reps; ++c) {
+        const int wq = wide ? ((head / per) * nkv + c) * per + head % per : head;
+        for (int i = lane; i < D; i += 32) kf_store(q_out, ((size_t)t * nq + wq) * D + i, 0.f);
+      }
+    return;
+  }
+  if (kind != 0 && !write_kv) return;
+  const int d = kind == 2 ? dv : dk;
+  const float* src = in + (size_t)t * ld + col0 + (kind == 0 ? head * dk : (kind == 1 ? (nh + head) * dk : (nh + nkv) * dk + head * dv));
+  float* x = hs[warp];
+  for (int i = lane; i < d; i += 32) x[i] = src[i];
+  __syncwarp();
+  const int half = rot >> 1;
+  float ss = 0.f;
+  float v[HM_MAX_D / 32];
+#pragma unroll
+  for (int k = 0; k < HM_MAX_D / 32; ++k) {
+    const int i = lane + 32 * k;
+    float y = 0.f;
+    if (i < d) {
+      y = x[i];
+      if (kind != 2 && i < rot) {
+        const float* c = cos_t + (size_t)t * half;
+        const float* s = sin_t + (size_t)t * half;
+        y = i < half ? x[i] * (c[i] * mag) - x[i + half] * (s[i] * mag) : x[i] * (c[i - half] * mag) + x[i - half] * (s[i - half] * mag);
+      }
+      ss = fmaf(y, y, ss);
+    }
+    v[k] = y;
+  }
+  if (kind != 2 && unit_norm) {
+    ss = kf_warp_sum(ss);
+    const float inv = 1.f / sqrtf(ss / (float)d + eps);
+#pragma unroll
+    for (int k = 0; k < HM_MAX_D / 32; ++k) v[k] *= inv;
+  }
+  int page = -1, in_page = 0;
+  if (kind != 0) {
+    const int pos = positions[t];
+    page = block_table[(size_t)req * table_stride + pos / page_size];
+    in_page = pos % page_size;
+    if (page < 0) return;                                   // never for a reserved position; guards the store
+  }
+  for (int c = 0; c < reps; ++c) {
+    if (kind == 0) {
+      const int wq = wide ? ((head / per) * nkv + c) * per + head % per : head;
+      TQ* o = q_out + ((size_t)t * nq + wq) * D;
+#pragma unroll
+      for (int k = 0; k < HM_MAX_D / 32; ++k) {
+        const int i = lane + 32 * k;
+        if (i < D) kf_store(o, i, v[k]);
+      }
+    } else {
+      const int st = wide ? (kind == 1 ? head * nkv + c : c * nkv + head) : head;
+      TKV* o = pages + ((((size_t)page * 2 + (kind - 1)) * nst + st) * page_size + in_page) * D;
+#pragma unroll
+      for (int k = 0; k < HM_MAX_D / 32; ++k) {
+        const int i = lane + 32 * k;
+        if (i < D) kf_store(o, i, v[k]);
+      }
+    }
+  }
+}
+
+KF_API int kf_rotate_norm_append(const float* in, int ld, int col0, const float* cos_t, const float* sin_t, int rot, float mag,
+                                 int unit_norm, float eps, int nh, int nkv, int dk, int dv, int D, int wide,
+                                 const int* positions, const int* row_req, const int* block_table, int table_stride,
+                                 int page_size, void* pages, int kv_dtype, void* q_out, int q_dtype, int write_kv, int T,
+                                 cudaStream_t stream) {
+  if (T <= 0) return KF_OK;
+  if (D > HM_MAX_D || dk > D || dv > D || dk < 1 || dv < 1 || rot > dk || (rot & 1) || nkv < 1 || nh % nkv) return KF_ERR_SIZE;
+  if (rot > 0 && (!cos_t || !sin_t)) return KF_ERR_SIZE;
+  const long n_work = (long)T * (nh + 2 * nkv);
+  const dim3 grid((unsigned)((n_work + HM_WARPS - 1) / HM_WARPS));
+#define KF_GO(TQ, TKV)                                                                                                   \
+  kf_launch(rotate_norm_append_kernel<TQ, TKV>, grid, dim3(HM_WARPS * 32), 0, stream, in, ld, col0, cos_t, sin_t, rot, mag, \
+            unit_norm, eps, nh, nkv, dk, dv, D, wide, positions, row_req, block_table, table_stride, page_size,           \
+            (TKV*)pages, (TQ*)q_out, write_kv, T)
+  if (q_dtype == KF_F32 && kv_dtype == KF_F32) KF_GO(float, float);
+  else if (q_dtype == KF_BF16 && kv_dtype == KF_BF16) KF_GO(__nv_bfloat16, __nv_bfloat16);
+  else return KF_ERR_DTYPE;
+#undef KF_GO
+  KF_CHECK_LAUNCH();
+  return KF_OK;
+}
+
+template <typename TQ, typename TW>
+__global__ void head_mix_gate_kernel(const TQ* __restrict__ o, const TW* __restrict__ mix, const float* __restrict__ g, int ld,
+                                     int gcol0, int nh, int nkv, int dv, int D, TQ* __restrict__ out,
+                                     const int* __restrict__ row_req) {
+  kf_pdl_trigger();
+  kf_pdl_wait();
+  extern __shared__ float ms[];                             // the mixing matrix [nh, nh]
+  if (mix)
+    for (int i = threadIdx.x; i < nh * nh; i += blockDim.x) ms[i] = kf_load(mix, i);
+  __syncthreads();
+  const int t = blockIdx.x;
+  const bool pad = row_req[t] < 0;
+  const int per = nh / nkv;
+  const int nq = mix ? nh * nkv : nh;
+  for (int e = threadIdx.x; e < nh * dv; e += blockDim.x) {
+    const int h = e / dv, i = e - h * dv;
+    float v = 0.f;
+    if (!pad) {
+      if (mix) {
+        const int cv = h / per;
+        for (int gq = 0; gq < nh; ++gq) {
+          const int wq = ((gq / per) * nkv + cv) * per + gq % per;
+          v = fmaf(ms[h * nh + gq], kf_load(o, ((size_t)t * nq + wq) * D + i), v);
+        }
+      } else {
+        v = kf_load(o, ((size_t)t * nq + h) * D + i);
+      }
+      if (g) v *= 1.f / (1.f + expf(-g[(size_t)t * ld + gcol0 + e]));
+    }
+    kf_store(out, (size_t)t * nh * dv + e, v);
+  }
+}
+
+KF_API int kf_head_mix_gate(const void* o, const void* mix, int w_dtype, const float* g, int ld, int gcol0, int nh, int nkv,
+                            int dv, int D, void* out, int dtype, const int* row_req, int T, cudaStream_t stream) {
+  if (T <= 0) return KF_OK;
+  if (nkv < 1 || nh % nkv || dv > D || nh > 128) return KF_ERR_SIZE;
+  const int threads = nh * dv >= 1024 ? 256 : 128;
+  const size_t smem = mix ? (size_t)nh * nh * sizeof(float) : 0;
+#define KF_GO(TQ, TW)                                                                                                \
+  kf_launch(head_mix_gate_kernel<TQ, TW>, dim3(T), dim3(threads), smem, stream, (const TQ*)o, (const TW*)mix, g, ld, gcol0, \
+            nh, nkv, dv, D, (TQ*)out, row_req)
+  if (dtype == KF_F32 && w_dtype == KF_F32) KF_GO(float, float);
+  else if (dtype == KF_BF16 && w_dtype == KF_BF16) KF_GO(__nv_bfloat16, __nv_bfloat16);
+  else if (dtype == KF_BF16 && w_dtype == KF_F32) KF_GO(__nv_bfloat16, float);
+  else if (dtype == KF_F32 && w_dtype == KF_BF16) KF_GO(float, __nv_bfloat16);
+  else return KF_ERR_DTYPE;
+#undef KF_GO
+  KF_CHECK_LAUNCH();
+  return KF_OK;
+}

@@ -239,6 +239,18 @@ def check_attention_sizes(n_heads: int, n_kv_heads: int, head_dim: int) -> None:
         raise KernelError(f"n_heads {n_heads} must be a multiple of n_kv_heads {n_kv_heads}")
 
 
+KERNEL_HEAD_SIZES = (16, 32, 64, 128, 256)
+
+
+def attention_head_size(n: int) -> int:
+    """The smallest head size the tensor-core attention kernels take that holds `n` elements (heads are stored with zero
+    tails up to it)."""
+    for d in KERNEL_HEAD_SIZES:
+        if n <= d:
+            return d
+    raise KernelError(f"heads of {n} elements are above {MAX_HEAD_DIM}, the largest the attention kernels take")
+
+
 # ---- operations -----------------------------------------------------------------------------------------
 
 @_dispatch("embed")
@@ -675,6 +687,74 @@ def add2_rmsnorm(a, b, x, *, next_weight=None, next_eps: float = 0.0, next_plus_
                                      _dt(next_out) if next_out is not None else F32, T, H, _stream()), "add2_rmsnorm")
 
 
+# ---- norms in groups, the polynomial activation, attention whose heads' weights are mixed ---------------------------------
+
+@_dispatch("group_rmsnorm")
+def group_rmsnorm(x, weight, eps: float, groups: int, out, rows=None) -> None:
+    """The row (x[rows[r]] if rows is given else x[r]) cut into `groups` equal parts, each divided by its own
+    sqrt(mean(part^2) + eps), times weight."""
+    n, H = out.shape
+    _check(library().kf_group_rmsnorm(_p(x), _p(weight), _dt(weight), _f(eps), int(groups), _p(out), _dt(out), _p(rows), n, H,
+                                      _stream()), "group_rmsnorm")
+
+
+@_dispatch("add_group_rmsnorm")
+def add_group_rmsnorm(branch, weight, eps: float, groups: int, residual, *, shift=None, next_weight=None, next_eps: float = 0.0,
+                      next_out=None) -> None:
+    """residual += group norm of branch (when branch is given); residual += shift, a constant row (when given);
+    next_out = group norm of the residual with next_weight (when given).  One kernel; both norms cut rows alike."""
+    T, H = residual.shape
+    ws = [w for w in (weight, shift, next_weight) if w is not None]
+    if len({w.dtype for w in ws}) > 1:
+        raise KernelError("add_group_rmsnorm: weights and shift must share one element type")
+    _check(library().kf_add_group_rmsnorm(_p(branch), _p(weight), _dt(ws[0]) if ws else F32, _f(eps), _p(residual), _p(shift),
+                                          _p(next_weight), _f(next_eps), _p(next_out),
+                                          _dt(next_out) if next_out is not None else F32, int(groups), T, H, _stream()),
+           "add_group_rmsnorm")
+
+
+@_dispatch("poly_norm")
+def poly_norm(z, coef, eps: float, out) -> None:
+    """out = a N(z) + b N(z^2) + c N(z^3) + e with (a, b, c, e) = coef and N(u) = u / sqrt(mean(u^2) + eps) over a row;
+    z 32-bit [T, I]."""
+    T, I = out.shape
+    _check(library().kf_poly_norm(_p(z), _p(coef), _dt(coef), _f(eps), _p(out), _dt(out), T, I, _stream()), "poly_norm")
+
+
+@_dispatch("rotate_norm_append")
+def rotate_norm_append(proj, col0: int, cos, sin, rot: int, magnitude: float, unit_norm: bool, eps: float, n_heads: int,
+                       n_kv_heads: int, key_dim: int, value_dim: int, wide: bool, ctx, cache, q_out) -> None:
+    """From the 32-bit q|k|v projection (columns col0.. of proj) to the attention's operands: q and k turned in pairs
+    (i, i + rot/2) by cos/sin * magnitude, then (unit_norm) divided by sqrt(mean(head^2) + eps); q into q_out, k and v
+    into the pages of `cache`, heads of D = the pages' head size with zero tails.  `wide`: every query head is stored
+    once per value head and the pages hold n_kv_heads^2 heads, (key head, value head) pairs, so that the attention
+    kernels give every query head's weighted sum over every value head (see `head_mix_gate`)."""
+    T = q_out.shape[0]
+    D = cache.pages.shape[-1]
+    reps = n_kv_heads if wide else 1
+    if q_out.shape[1] != n_heads * reps * D or cache.pages.shape[2] != n_kv_heads * reps:
+        raise KernelError(f"rotate_norm_append: q rows of {q_out.shape[1]} and pages of {cache.pages.shape[2]} heads do not fit "
+                          f"{n_heads} x {reps} query heads and {n_kv_heads} x {reps} stored heads of {D}")
+    table = ctx.block_tables[cache.group]
+    _check(library().kf_rotate_norm_append(_p(proj), proj.shape[1], int(col0), _p(cos), _p(sin), int(rot), _f(magnitude),
+                                           int(bool(unit_norm)), _f(eps), n_heads, n_kv_heads, key_dim, value_dim, D, int(bool(wide)),
+                                           _p(ctx.positions), _p(ctx.row_req), _p(table), table.shape[1], cache.page_size,
+                                           _p(cache.pages), _dt(cache.pages), _p(q_out), _dt(q_out), int(cache.writes), T,
+                                           _stream()), "rotate_norm_append")
+
+
+@_dispatch("head_mix_gate")
+def head_mix_gate(o, mix, proj, gate_col0: int, n_heads: int, n_kv_heads: int, value_dim: int, head_dim: int, out, ctx) -> None:
+    """out[t, h * value_dim + e] = sigmoid(proj[t, gate_col0 + h * value_dim + e]) * sum_g mix[h, g] * o[t, wide(g, kv(h)), e]:
+    `o` holds, for every query head g and value head c, head g's weighted sum over the values of c (the attention's result
+    over operands laid out by `rotate_norm_append(wide=True)`), wide(g, c) = ((g // r) * n_kv_heads + c) * r + g % r with
+    r = n_heads / n_kv_heads, kv(h) = h // r.  mix None: no mixing (o holds n_heads heads); proj None: no gate."""
+    T = out.shape[0]
+    _check(library().kf_head_mix_gate(_p(o), _p(mix), _dt(mix) if mix is not None else F32, _p(proj),
+                                      proj.shape[1] if proj is not None else 0, int(gate_col0), n_heads, n_kv_heads, value_dim,
+                                      head_dim, _p(out), _dt(out), _p(ctx.row_req), T, _stream()), "head_mix_gate")
+
+
 # ---- the gated delta rule, latent attention, layer scales, per-token side inputs, mixtures of experts ------------------
 
 @_dispatch("linear_cols")
@@ -769,13 +849,19 @@ def head_linear(x, col0: int, weight, out) -> None:
 
 
 @_dispatch("moe_route")
-def moe_route(logits, correction, groups: int, keep: int, top: int, scale: float, ids, weights) -> None:
-    """For every row of 32-bit router logits [T, E]: s = sigmoid(logits); the choice is made on s + correction, among the
-    experts of the `keep` groups (of `groups` equal groups of neighbours) whose two largest choice scores sum highest;
-    ids [T, top] int32 = the `top` largest; weights [T, top] = s of the chosen / (their sum + 1e-20) * scale."""
+def moe_route(logits, correction, groups: int, keep: int, top: int, scale: float, ids, weights, *, score: str = "sigmoid",
+              group_rank: str = "best_two", normalize: bool = True) -> None:
+    """For every row of 32-bit router logits [T, E]: s = sigmoid(logits) (or, score 'softmax', the softmax over all
+    experts); the choice is made on s + correction, among the experts of the `keep` groups (of `groups` equal groups of
+    neighbours) whose two largest choice scores sum highest (group_rank 'best': whose largest is highest);
+    ids [T, top] int32 = the `top` largest; weights [T, top] = s of the chosen * scale, divided by their sum + 1e-20
+    when `normalize`."""
     T, E = logits.shape
+    if score not in ("sigmoid", "softmax") or group_rank not in ("best_two", "best"):
+        raise KernelError(f"moe_route: score {score!r} / group_rank {group_rank!r} are not known")
     _check(library().kf_moe_route(_p(logits), _p(correction), _dt(correction) if correction is not None else F32, T, E,
-                                  int(groups), int(keep), int(top), _f(scale), _p(ids), _p(weights), _stream()), "moe_route")
+                                  int(groups), int(keep), int(top), _f(scale), int(score == "softmax"),
+                                  int(group_rank == "best"), int(bool(normalize)), _p(ids), _p(weights), _stream()), "moe_route")
 
 
 @_dispatch("moe_plan")
@@ -797,17 +883,21 @@ def moe_plan(ids, n_experts: int, ctx) -> dict:
 
 
 @_dispatch("moe_linear")
-def moe_linear(x, plan: dict, weight, out, *, gather: bool, gated: bool = False, limit: float = 0.0) -> None:
+def moe_linear(x, plan: dict, weight, out, *, gather: bool, gated: bool = False, limit: float = 0.0,
+               activation: str = "clamped_swish") -> None:
     """out[r] = x_r . weight[e(r)]^T for every sorted pair r of the plan, e(r) its expert; weight [E, N (or 2N: gate rows
     then up rows, when gated), K].  `gather`: x holds one row per TOKEN and pair r reads the row of its token; otherwise
-    x holds one row per sorted pair.  gated: out = the clamped gated activation of (gate, up) with `limit`."""
+    x holds one row per sorted pair.  gated: out = the clamped gated activation of (gate, up) with `limit`, or, with
+    activation 'silu', gate * sigmoid(gate) * up."""
+    if gated and activation not in ("clamped_swish", "silu"):
+        raise KernelError(f"moe_linear: gated activation {activation!r} is not one of clamped_swish, silu")
     E, NW, K = weight.shape
     N = NW // 2 if gated else NW
     if out.shape[0] != plan["pairs"] or out.shape[1] != N or x.shape[1] != K:
         raise KernelError(f"moe_linear: x{tuple(x.shape)} weight{tuple(weight.shape)} out{tuple(out.shape)} do not agree")
     tiles = (plan["tile_group"], plan["tile_row0"], plan["tile_nrows"], plan["n_tiles"])
     _grouped(x, 0, K, 0, plan["sorted_pair"] if gather else None, plan["top"] if gather else 1, weight, NW * K, out, 0, N, 0,
-             tiles, plan["max_tiles"], E, plan["pairs"], N, K, int(gated), limit, "moe_linear")
+             tiles, plan["max_tiles"], E, plan["pairs"], N, K, (2 if activation == "silu" else 1) if gated else 0, limit, "moe_linear")
 
 
 @_dispatch("moe_combine")

@@ -152,3 +152,83 @@ class ConvGatedAttention(Mixer):
 
 
 register_mixer("conv_gated_attention", ConvGatedAttention)
+
+
+class TalkingAttention(Mixer):
+    """Grouped-query attention with unit-norm queries and keys, whose softmax weights are mixed across heads after the
+    softmax, and whose heads are gated element by element on their way out.  In order, for the normed input x:
+
+      [q | k | v | g] = x W_in^T                                one product over the stacked matrix
+      q, k <- rotation of the first rotary dims by `position`, pairs (i, i + rot/2), cos and sin times its `magnitude`
+      q, k <- head / sqrt(mean(head^2) + norm_eps)              after the rotation, no weight (`unit_norm`)
+      a_h(i, .) = softmax_j(q_h(i) . k_(h/r)(j) * scale), causal, optionally windowed;  r = n_heads / n_kv_heads
+      b_h = sum_g mix[h, g] a_g                                 the heads' weights mixed (`mix` [n_heads, n_heads])
+      o_h(i) = sum_j b_h(i, j) v_(h/r)(j)
+      o <- o * sigmoid(g)                                       one gate per element, from the same input x
+      y = o W_o^T
+
+    Since o_h = sum_g mix[h, g] O[g, h/r] with O[g, c] the plain attention of query head g over value head c, the
+    framework's attention kernels do the work on "wide" operands: every query head once per value head, and the cache
+    holding (key head, value head) pairs; `ops.head_mix_gate` then sums over g and gates.  The cache therefore holds
+    n_kv_heads^2 heads of D = max(key_dim, value_dim).  With `mix` None the mixer is plain grouped-query attention with
+    the same extras.  Scores, softmax, norms, rotation, mixing sums and the gate are 32-bit."""
+
+    def __init__(self, w_in: torch.Tensor, wo: torch.Tensor, *, n_heads: int, n_kv_heads: int, key_dim: int, value_dim: int,
+                 scale: float, window: int | None = None, position: PositionEncoding | None = None,
+                 mix: torch.Tensor | None = None, unit_norm: bool = True, norm_eps: float = 1e-6, gated: bool = True):
+        if n_heads % n_kv_heads:
+            raise ValueError(f"n_heads {n_heads} is not a multiple of n_kv_heads {n_kv_heads}")
+        self.wo, self.mix = wo, mix
+        self.n_heads, self.n_kv_heads = int(n_heads), int(n_kv_heads)
+        self.key_dim, self.value_dim = int(key_dim), int(value_dim)
+        self.head_dim = ops.attention_head_size(max(self.key_dim, self.value_dim))
+        self.scale = float(scale)
+        self.window = None if window is None else int(window)
+        self.position = position
+        self.unit_norm, self.norm_eps, self.gated = bool(unit_norm), float(norm_eps), bool(gated)
+        self.reps = self.n_kv_heads if mix is not None else 1
+        self.qkv_width = (self.n_heads + self.n_kv_heads) * self.key_dim + self.n_kv_heads * self.value_dim
+        self.proj_width = self.qkv_width + (self.n_heads * self.value_dim if self.gated else 0)
+        self.width = wo.shape[0]
+        if w_in.numel() and w_in.shape[0] != self.proj_width:
+            raise ValueError(f"stacked projection has shape {tuple(w_in.shape)}, expected {self.proj_width} rows")
+        if mix is not None and mix.numel() and tuple(mix.shape) != (self.n_heads, self.n_heads):
+            raise ValueError(f"the mixing matrix has shape {tuple(mix.shape)}, expected {(self.n_heads, self.n_heads)}")
+        self.w_in = pad_rows(w_in)
+        self.proj_width = max(self.proj_width, self.w_in.shape[0])
+        rot = getattr(position, "rotary_dims", 0) if position is not None else 0
+        if rot > self.key_dim:
+            raise ValueError(f"{rot} rotary dims for keys of {self.key_dim}")
+        if position is not None and getattr(position, "interleaved", False):
+            raise ValueError("this mixer turns pairs (i, i + rot/2); an interleaved rotation is not supported")
+        ops.check_attention_sizes(self.n_heads * self.reps, self.n_kv_heads * self.reps, self.head_dim)
+
+    def state_need(self):
+        return PagedKV(self.n_kv_heads * self.reps, self.head_dim, self.window)
+
+    def forward(self, x, ctx, cache):
+        T = x.shape[0]
+        nh, nkv, D, reps = self.n_heads, self.n_kv_heads, self.head_dim, self.reps
+        proj = ctx.buf("attn_proj", (T, self.proj_width), torch.float32)
+        ops.linear(x, self.w_in, proj)
+        if self.position is not None:
+            cos, sin = self.position.rotation(ctx)
+            rot, mag = 2 * cos.shape[1], float(getattr(self.position, "magnitude", 1.0))
+        else:
+            cos = sin = None
+            rot, mag = 0, 1.0
+        q = ctx.buf("attn_q", (T, nh * reps * D), ctx.act_dtype)
+        ops.rotate_norm_append(proj, 0, cos, sin, rot, mag, self.unit_norm, self.norm_eps, nh, nkv, self.key_dim,
+                               self.value_dim, self.mix is not None, ctx, cache, q)
+        o = ctx.buf("attn_o", (T, nh * reps * D), ctx.act_dtype)
+        ops.paged_attention(q, o, ctx, cache, nh * reps, nkv * reps, D, self.scale, 0.0, self.window)
+        if self.mix is not None or self.gated or D != self.value_dim:
+            packed = ctx.buf("attn_gated", (T, nh * self.value_dim), ctx.act_dtype)
+            ops.head_mix_gate(o, self.mix, proj if self.gated else None, self.qkv_width, nh, nkv, self.value_dim, D, packed, ctx)
+            o = packed
+        y = ctx.buf("branch_out", (T, self.width), torch.float32)
+        ops.linear(o, self.wo, y)
+        return y
+
+
+register_mixer("talking_attention", TalkingAttention)

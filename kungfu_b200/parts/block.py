@@ -4,7 +4,7 @@
 `Residual` with a post norm, two of them per block, gemma2.rs:39-41):
   h   = x + post_mixer(mixer(pre_mixer(x)))
   out = h + post_ffn(ffn(pre_ffn(h)))
-A post norm of None gives the plain pre-norm block other models use.
+A post norm of None gives the plain pre-norm block other models use; `ffn` None a layer of the first line alone.
 The residual stream and its sums stay in 32-bit.
 """
 from __future__ import annotations
@@ -20,7 +20,7 @@ class SandwichBlock(Block):
     fuses_next_norm = True
 
     def __init__(self, pre_mixer: Norm, mixer: Mixer, post_mixer: Norm | None,
-                 pre_ffn: Norm, ffn: FeedForward, post_ffn: Norm | None):
+                 pre_ffn: Norm | None, ffn: FeedForward | None, post_ffn: Norm | None):
         self.pre_mixer, self.mixer, self.post_mixer = pre_mixer, mixer, post_mixer
         self.pre_ffn, self.ffn, self.post_ffn = pre_ffn, ffn, post_ffn
 
@@ -28,6 +28,11 @@ class SandwichBlock(Block):
         act = ctx.act_dtype
         n = normed if normed is not None else self.pre_mixer.forward(x, ctx, act)
         a = self.mixer.forward(n, ctx, cache)
+        if self.ffn is None:                                   # a layer without a feed-forward
+            if self.post_mixer is not None:
+                return x, self.post_mixer.add_into(a, x, ctx, then=then, out_dtype=act if then is not None else None)
+            ops.add(a, x)
+            return x, (then.forward(x, ctx, act) if then is not None else None)
         if self.post_mixer is not None:
             n = self.post_mixer.add_into(a, x, ctx, then=self.pre_ffn, out_dtype=act)
         else:

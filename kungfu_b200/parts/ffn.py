@@ -71,3 +71,32 @@ class DenseFfn(FeedForward):
 
 
 register_feed_forward("dense", DenseFfn)
+
+
+class PolyNormFfn(FeedForward):
+    """A feed-forward without a gate whose activation norms the powers of its input:
+    y = act(x Wup^T) Wdown^T,  act(z) = a N(z) + b N(z^2) + c N(z^3) + e,  N(u) = u / sqrt(mean(u^2) + eps) over a token's
+    row, powers element by element, (a, b, c, e) = `coef`.  The up product leaves 32-bit rows; sums and factors are 32-bit."""
+
+    def __init__(self, w_up: torch.Tensor, w_down: torch.Tensor, coef: torch.Tensor, eps: float):
+        if w_up.dim() == 2 and w_down.dim() == 2 and w_up.shape[0] != w_down.shape[1]:
+            raise ValueError("the up matrix must have as many rows as the down matrix has columns")
+        if coef.numel() not in (0, 4):
+            raise ValueError(f"the activation takes four numbers, found {coef.numel()}")
+        self.w_up, self.w_down, self.coef = w_up, w_down, coef
+        self.eps = float(eps)
+        self.inner = w_down.shape[1] if w_down.dim() == 2 else 0
+        self.width = w_down.shape[0]
+
+    def forward(self, x, ctx):
+        T = x.shape[0]
+        z = ctx.buf("ffn_up", (T, self.inner), torch.float32)
+        ops.linear(x, self.w_up, z)
+        h = ctx.buf("ffn_h", (T, self.inner), ctx.act_dtype)
+        ops.poly_norm(z, self.coef, self.eps, h)
+        y = ctx.buf("ffn_out", (T, self.width), torch.float32)
+        ops.linear(h, self.w_down, y)
+        return y
+
+
+register_feed_forward("poly_norm", PolyNormFfn)

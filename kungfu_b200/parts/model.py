@@ -4,6 +4,8 @@ The order in which blocks run is data (`schedule`): a list of `LayerCall`s.  A c
 names the block to run and the cache slot it uses.  A block may be named twice (each
 call then has its own cache slot), and a call may read a slot that an earlier call
 wrote (`writes=False`, the reference's `kv_source`, crates/kf-layers/src/attention.rs:106-107).
+A call may also name a constant row that is added to the residual right before it (`shift`): models that run a
+stretch of layers several times mark each pass that way.
 The model reports what each cache slot must hold (`state_needs`); the cache manager
 reads only that (reference: `Layer::states`, crates/kf-core/src/layer.rs:20-27).
 Reference for the pass itself: crates/kf-layers/src/model.rs:105-180.
@@ -22,6 +24,7 @@ class LayerCall:
     layer: int                 # index into `layers`
     cache: int                 # cache slot this call uses
     writes: bool = True        # False: reads a slot another call filled in this step
+    shift: object = None       # a [width] tensor added to every row of the residual right before this call (else None)
 
 
 def default_schedule(n_layers: int) -> list[LayerCall]:
@@ -65,9 +68,18 @@ class DecoderModel(Part):
             block = self.layers[call.layer]
             view = ctx.cache_view(call.cache, call.writes)
             with ops.nvtx_range(f"layer {call.layer} ({type(block.mixer).__name__})"):
+                if call.shift is not None:
+                    pre = getattr(block, "pre_mixer", None) if getattr(block, "fuses_next_norm", False) else None
+                    if hasattr(pre, "after_shift"):
+                        normed = pre.after_shift(x, call.shift, ctx, ctx.act_dtype)      # the add and the norm in one kernel
+                    else:
+                        ops.add_group_rmsnorm(None, None, 0.0, 1, x, shift=call.shift)
+                        normed = None
                 if getattr(block, "fuses_next_norm", False):
-                    # the last kernel of this block also computes the next block's first norm, when both can
-                    nxt = self.layers[self.schedule[i + 1].layer] if i + 1 < len(self.schedule) else None
+                    # the last kernel of this block also computes the next block's first norm, when both can and
+                    # nothing is added to the residual in between
+                    nxt_call = self.schedule[i + 1] if i + 1 < len(self.schedule) else None
+                    nxt = self.layers[nxt_call.layer] if nxt_call is not None and nxt_call.shift is None else None
                     then = nxt.pre_mixer if nxt is not None and getattr(nxt, "fuses_next_norm", False) else None
                     x, normed = block.forward(x, ctx, view, normed=normed, then=then)
                 else:

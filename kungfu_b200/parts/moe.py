@@ -21,8 +21,16 @@ from .base import FeedForward, register_feed_forward
 
 class RoutedExperts(FeedForward):
     def __init__(self, w_router: torch.Tensor, correction: torch.Tensor | None, w_gate_up: torch.Tensor, w_down: torch.Tensor, *,
-                 top: int, scale: float, limit: float, groups: int = 1, keep: int = 1, shared: FeedForward | None = None):
-        """w_gate_up [E, 2 ff, width] (gate rows, then up rows, per expert), w_down [E, width, ff]."""
+                 top: int, scale: float, limit: float, groups: int = 1, keep: int = 1, shared: FeedForward | None = None,
+                 score: str = "sigmoid", group_rank: str = "best_two", normalize: bool = True,
+                 activation: str = "clamped_swish"):
+        """w_gate_up [E, 2 ff, width] (gate rows, then up rows, per expert), w_down [E, width, ff].
+        Other mixtures of the same shape: `score` 'softmax' (scores = the softmax of z over all experts), `group_rank`
+        'best' (a group scores its largest member), `normalize` False (the winners keep their scores as weights, times
+        `scale`), `activation` 'silu' (experts W_down [silu(g) u])."""
+        if score not in ("sigmoid", "softmax") or group_rank not in ("best_two", "best") or activation not in ("clamped_swish", "silu"):
+            raise ValueError(f"score {score!r}, group_rank {group_rank!r} or activation {activation!r} is not known")
+        self.score, self.group_rank, self.normalize, self.activation = score, group_rank, bool(normalize), activation
         self.w_router, self.correction = w_router, correction
         self.w_gate_up, self.w_down, self.shared = w_gate_up, w_down, shared
         self.top, self.scale, self.limit = int(top), float(scale), float(limit)
@@ -46,10 +54,11 @@ class RoutedExperts(FeedForward):
         ops.linear(x, self.w_router, logits)
         ids = ctx.buf("moe_ids", (T, top), torch.int32)
         wts = ctx.buf("moe_weights", (T, top), torch.float32)
-        ops.moe_route(logits, self.correction, self.groups, self.keep, top, self.scale, ids, wts)
+        ops.moe_route(logits, self.correction, self.groups, self.keep, top, self.scale, ids, wts, score=self.score,
+                      group_rank=self.group_rank, normalize=self.normalize)
         plan = ops.moe_plan(ids, E, ctx)
         h = ctx.buf("moe_h", (T * top, self.inner), ctx.act_dtype)
-        ops.moe_linear(x, plan, self.w_gate_up, h, gather=True, gated=True, limit=self.limit)
+        ops.moe_linear(x, plan, self.w_gate_up, h, gather=True, gated=True, limit=self.limit, activation=self.activation)
         eo = ctx.buf("moe_expert_out", (T * top, self.width), torch.float32)
         ops.moe_linear(h, plan, self.w_down, eo, gather=False)
         sh = self.shared.forward(x, ctx) if self.shared is not None else None

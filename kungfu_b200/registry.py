@@ -58,6 +58,9 @@ def _register_builtin() -> None:
     from .config.petanex import PetanexConfig
     from .models import petanex
     register("Petanex", PetanexConfig.from_dict, petanex.build, petanex.tensor_specs, replace=True)
+    from .config.pimodra import PimodraConfig
+    from .models import pimodra
+    register("Pimodra", PimodraConfig.from_dict, pimodra.build, pimodra.tensor_specs, replace=True)
 
 
 _register_builtin()

@@ -323,21 +323,109 @@ class CpuOps:
         xs = x[:T, col0:col0 + H * I].float().view(T, H, I)
         out.copy_(torch.einsum("thi,hoi->tho", xs, weight.float()).reshape(T, H * O).to(out.dtype))
 
-    def moe_route(self, logits, correction, groups, keep, top, scale, ids, weights):
+    def moe_route(self, logits, correction, groups, keep, top, scale, ids, weights, *, score="sigmoid", group_rank="best_two",
+                  normalize=True):
         T, E = logits.shape
-        s = torch.sigmoid(torch.nan_to_num(logits.float()))
+        z = torch.nan_to_num(logits.float())
+        s = torch.softmax(z, dim=-1) if score == "softmax" else torch.sigmoid(z)
         choice = s + (correction.float()[None, :] if correction is not None else 0.0)
         if groups > 1:
             per = E // groups
             g = choice.view(T, groups, per)
-            score = g.topk(min(2, per), dim=-1).values.sum(-1)
+            score = g.topk(min(1 if group_rank == "best" else 2, per), dim=-1).values.sum(-1)
             best = score.topk(keep, dim=-1).indices
             ok = torch.zeros(T, groups, dtype=torch.bool).scatter_(1, best, True)
             choice = choice.masked_fill(~ok[:, :, None].expand(T, groups, per).reshape(T, E), float("-inf"))
         pick = choice.topk(top, dim=-1).indices
         w = s.gather(1, pick)
         ids.copy_(pick.to(torch.int32))
-        weights.copy_(w / (w.sum(-1, keepdim=True) + 1e-20) * scale)
+        weights.copy_((w / (w.sum(-1, keepdim=True) + 1e-20) if normalize else w) * scale)
+
+    @staticmethod
+    def _gnorm(x, weight, eps, groups):
+        T, H = x.shape
+        p = x.float().reshape(T, groups, H // groups)
+        return (p * torch.rsqrt(p.pow(2).mean(-1, keepdim=True) + eps)).reshape(T, H) * weight.float()
+
+    def group_rmsnorm(self, x, weight, eps, groups, out, rows=None):
+        src = x if rows is None else x[rows.long()]
+        out.copy_(self._gnorm(src, weight, eps, groups).to(out.dtype))
+
+    def add_group_rmsnorm(self, branch, weight, eps, groups, residual, *, shift=None, next_weight=None, next_eps=0.0,
+                          next_out=None):
+        if branch is not None:
+            residual += self._gnorm(branch, weight, eps, groups)
+        if shift is not None:
+            residual += shift.float()[None, :]
+        if next_out is not None:
+            next_out.copy_(self._gnorm(residual, next_weight, next_eps, groups).to(next_out.dtype))
+
+    def poly_norm(self, z, coef, eps, out):
+        a, b, c, e = (float(v) for v in coef.float())
+        z = z.float()
+
+        def n(u):
+            return u * torch.rsqrt(u.pow(2).mean(-1, keepdim=True) + eps)
+
+        out.copy_((a * n(z) + b * n(z * z) + c * n(z * z * z) + e).to(out.dtype))
+
+    def rotate_norm_append(self, proj, col0, cos, sin, rot, magnitude, unit_norm, eps, nh, nkv, dk, dv, wide, ctx, cache, q_out):
+        T = q_out.shape[0]
+        D = cache.pages.shape[-1]
+        C = (nh + nkv) * dk + nkv * dv
+        x = proj[:, col0:col0 + C].float()
+        q = x[:, :nh * dk].reshape(T, nh, dk).clone()
+        k = x[:, nh * dk:(nh + nkv) * dk].reshape(T, nkv, dk).clone()
+        v = x[:, (nh + nkv) * dk:].reshape(T, nkv, dv)
+        for y in (q, k):
+            if rot:
+                c, s_ = cos[:, None, :] * magnitude, sin[:, None, :] * magnitude
+                a, b = y[..., :rot // 2].clone(), y[..., rot // 2:rot].clone()
+                y[..., :rot // 2] = a * c - b * s_
+                y[..., rot // 2:rot] = a * s_ + b * c
+            if unit_norm:
+                y.copy_(y * torch.rsqrt(y.pow(2).mean(-1, keepdim=True) + eps))
+        reps, per = (nkv if wide else 1), nh // nkv
+        qp = torch.zeros(T, nh * reps, D)
+        for g in range(nh):
+            for c in range(reps):
+                qp[:, ((g // per) * nkv + c) * per + g % per if wide else g, :dk] = q[:, g]
+        qp[ctx.row_req[:T] < 0] = 0
+        q_out.copy_(qp.reshape(T, nh * reps * D).to(q_out.dtype))
+        if not cache.writes:
+            return
+        table = ctx.block_tables[cache.group]
+        P = cache.page_size
+        for t in range(T):
+            r = int(ctx.row_req[t])
+            if r < 0:
+                continue
+            pos = int(ctx.positions[t])
+            page = int(table[r, pos // P])
+            assert page >= 0
+            cache.pages[page, :, :, pos % P, :] = 0
+            for ck in range(nkv):
+                for cv in range(reps):
+                    st = ck * nkv + cv if wide else ck
+                    cache.pages[page, 0, st, pos % P, :dk] = k[t, ck].to(cache.pages.dtype)
+                    cache.pages[page, 1, st, pos % P, :dv] = v[t, cv if wide else ck].to(cache.pages.dtype)
+
+    def head_mix_gate(self, o, mix, proj, gate_col0, nh, nkv, dv, D, out, ctx):
+        T = out.shape[0]
+        per = nh // nkv
+        if mix is None:
+            y = o.float().reshape(T, nh, D)[..., :dv].clone()
+        else:
+            wide = o.float().reshape(T, nh * nkv, D)[..., :dv]
+            y = torch.zeros(T, nh, dv)
+            for h in range(nh):
+                for g in range(nh):
+                    y[:, h] += mix[h, g].float() * wide[:, ((g // per) * nkv + h // per) * per + g % per]
+        y = y.reshape(T, nh * dv)
+        if proj is not None:
+            y = y * torch.sigmoid(proj[:, gate_col0:gate_col0 + nh * dv].float())
+        y[ctx.row_req[:T] < 0] = 0
+        out.copy_(y.to(out.dtype))
 
     def moe_plan(self, ids, n_experts, ctx):
         T, top = ids.shape
@@ -348,7 +436,7 @@ class CpuOps:
         return {"pairs": T * top, "top": top, "sorted_pair": order.to(torch.int32), "inverse": inverse.to(torch.int32),
                 "expert_of_sorted": flat[order]}
 
-    def moe_linear(self, x, plan, weight, out, *, gather, gated=False, limit=0.0):
+    def moe_linear(self, x, plan, weight, out, *, gather, gated=False, limit=0.0, activation="clamped_swish"):
         top = plan["top"]
         for r in range(plan["pairs"]):
             e = int(plan["expert_of_sorted"][r])
@@ -356,7 +444,7 @@ class CpuOps:
             y = weight[e].float() @ row.float()
             if gated:
                 N = y.shape[0] // 2
-                y = self._clamped(y[:N], y[N:], limit)
+                y = y[:N] * torch.sigmoid(y[:N]) * y[N:] if activation == "silu" else self._clamped(y[:N], y[N:], limit)
             out[r] = y.to(out.dtype)
 
     def moe_combine(self, expert_out, plan, weights, shared, y):
