@@ -7,6 +7,7 @@
                     (kernels alone, JSON lines; for the summaries in profiles/)
     python bench.py --compare bolonex
     python bench.py --compare petanex
+    python bench.py --compare pimodra
                     (Bolonex beside Gemma 2, or Petanex beside Bolonex, at equal layer sizes: prefill and decode throughput
                     and, per operation, the time of one step against the time its bytes, or its multiply-adds, take at the
                     measured rates; one JSON line)
@@ -675,6 +676,60 @@ def compare_petanex(args) -> dict:
                                                                       ("bolonex", bolonex_config(z), bolonex_op_bytes)))
 
 
+# ---- Pimodra beside Gemma 2 at equal layer sizes (--compare pimodra) -------------------------------------------------
+# Eight layer runs in both: Pimodra has four layers (feed-forwards dense, mixture, dense, mixture) that run twice as one
+# looped stretch; the same width, heads, head size, dense feed-forward width and vocabulary; the mixture's chosen experts
+# together have the dense width.  Every layer's window is longer than the contexts measured, as the Gemma 2 twin's is, so
+# both attend to the same keys.  (The Gemma 2 feed-forward is gated: three matrices where Pimodra's dense one has two.)
+PIMODRA_SIZES = {
+    "w2048": dict(BOLONEX_SIZES["w2048"], experts=32, top=4, e_groups=4, e_keep=2),
+    "w4096": dict(BOLONEX_SIZES["w4096"], experts=64, top=8, e_groups=8, e_keep=4),
+}
+
+
+def pimodra_config(z: dict) -> dict:
+    att = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["dim"], "scale": z["dim"] ** -0.5,
+           "mask": {"size": 1 << 20},
+           "rot": {"base": 10000.0, "dims": z["dim"], "scaling": {"factor": 4.0, "original": 2048, "fast": 32.0, "slow": 1.0}}}
+    eff = z["ff"] // z["top"] // 64 * 64
+    dense = {"kind": "dense", "ff": z["ff"]}
+    moe = {"kind": "moe", "expert": {"ff": eff},
+           "router": {"experts": z["experts"], "top": z["top"], "groups": {"count": z["e_groups"], "keep": z["e_keep"]}}}
+    layers = [{"type": "attention", "mixer": att, "mlp": dense if i % 2 == 0 else moe} for i in range(COMPARE_LAYERS // 2)]
+    return {"architecture": "Pimodra", "width": z["width"], "vocab": COMPARE_VOCAB, "norm": {"eps": 1e-5, "groups": 8},
+            "loop": {"start": 0, "stop": COMPARE_LAYERS // 2, "times": 2}, "layers": layers}
+
+
+def pimodra_op_bytes(z: dict, T: int, n_reqs: int, keys: int) -> dict:
+    """Bytes (and, for the grouped products, floating-point operations) each operation of one Pimodra step must move,
+    summed over the layer runs that use it.  The attention's entry is the same as the Gemma 2 twin's: the keys and values
+    once, the queries and the result."""
+    W, H, G, d, ff, L = z["width"], z["heads"], z["kv_heads"], z["dim"], z["ff"], COMPARE_LAYERS
+    cq = (H + 2 * G) * d
+    n_moe = L // 2
+    n_dense = L - n_moe
+    eff = ff // z["top"] // 64 * 64
+    P = T * z["top"]
+    used = min(z["experts"], P)
+    return {
+        "rotate_norm_append": L * T * (4 * cq + 2 * cq + 4 * d),
+        "paged_attention": L * (n_reqs * keys * 2 * G * d * 2 + T * H * d * 4),
+        "head_mix_gate": L * T * H * d * (2 * G + 4 + 2),
+        "add_group_rmsnorm": (2 * L + 2) * T * W * 14,
+        "group_rmsnorm": T * W * 6,
+        "poly_norm": n_dense * T * ff * 6,
+        "moe_route": n_moe * T * (z["experts"] * 4 + z["top"] * 8),
+        "moe_plan": n_moe * P * 12,
+        "moe_linear": (n_moe * (used * 3 * eff * W * 2 + P * (2 * W + 4 * eff + 4 * W)), n_moe * 6 * P * eff * W),
+        "moe_combine": n_moe * T * W * (4 * z["top"] + 8),
+    }
+
+
+def compare_pimodra(args) -> dict:
+    return compare_models(args, "pimodra", PIMODRA_SIZES, lambda z: (("pimodra", pimodra_config(z), pimodra_op_bytes),
+                                                                      ("gemma2", gemma_twin_config(z), gemma_op_bytes)))
+
+
 def micro_attention() -> int:
     """Decode attention alone: eight launches over distinct pages replayed from a CUDA graph, per batch size; one JSON
     line each with microseconds per launch and bytes of keys and values over that time."""
@@ -1088,14 +1143,14 @@ def main() -> int:
     ap.add_argument("--only-headline", action="store_true", help="skip the other batch sizes, the mixed steps, 32-bit and the other model sizes")
     ap.add_argument("--micro", choices=["attention", "prompt-attention", "gemm", "products", "qkv-rope", "reference"],
                     help="time kernels alone instead of the model step")
-    ap.add_argument("--compare", choices=["bolonex", "petanex"],
-                    help="another workload: Bolonex beside Gemma 2, or Petanex beside Bolonex, at equal layer sizes (prefill, "
-                         "decode, per-operation rooflines)")
+    ap.add_argument("--compare", choices=["bolonex", "petanex", "pimodra"],
+                    help="another workload: Bolonex beside Gemma 2, Petanex beside Bolonex, or Pimodra beside Gemma 2, at equal "
+                         "layer sizes (prefill, decode, per-operation rooflines)")
     args = ap.parse_args()
     if args.compare:
         args.warmup = max(args.warmup, 3)
         args.reps = max(args.reps, 1)
-        print(json.dumps(compare_petanex(args) if args.compare == "petanex" else compare_bolonex(args)))
+        print(json.dumps({"bolonex": compare_bolonex, "petanex": compare_petanex, "pimodra": compare_pimodra}[args.compare](args)))
         return 0
     if args.micro:
         return {"attention": micro_attention, "prompt-attention": micro_prompt_attention, "gemm": micro_gemm,

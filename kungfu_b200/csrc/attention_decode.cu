@@ -162,7 +162,7 @@ __global__ void __launch_bounds__(DEC_WARPS * 32)
 attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ pages,
                    const int* __restrict__ items, int n_items, const int* __restrict__ positions,
                    const int* __restrict__ row_req, const int* __restrict__ table, int table_stride, int page_size,
-                   int nh, int nkv, float scale, float softcap, int window, int n_splits,
+                   int nh, int nkv, float scale, float softcap, int window, int vsplit, int n_splits,
                    float* __restrict__ partial, int* __restrict__ counters, __nv_bfloat16* __restrict__ out) {
   kf_pdl_trigger();
   kf_pdl_wait();
@@ -178,6 +178,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
   const int G = nh / nkv;
   const int h_first = kvh * G + hz * HT;                      // first query head of this block
   const int h_count = min(HT, G - hz * HT);
+  const KfHeadMap hm = kf_head_map(h_first, kvh, nh, nkv, vsplit);
   const int t = items ? items[item] : item;
   const int req = row_req[t];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -201,7 +202,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
 #pragma unroll
   for (int h = 0; h < HT; ++h) {
     if (h < h_count) {
-      const uint4 r = *reinterpret_cast<const uint4*>(q + ((size_t)t * nh + h_first + h) * D + chunk * 8);
+      const uint4 r = *reinterpret_cast<const uint4*>(q + ((size_t)t * hm.n_query + hm.query + h) * D + chunk * 8);
       unpack8(r, qf[h]);
 #pragma unroll
       for (int i = 0; i < 8; ++i) qf[h][i] *= scale;
@@ -220,7 +221,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
   }
   const int* tab = table + (size_t)req * table_stride;
   const size_t head_stride = (size_t)page_size * D;
-  const size_t v_off = (size_t)nkv * head_stride;             // from a key row to the value row of the same slot
+  const size_t v_off = (size_t)(hm.n_stored + hm.value - hm.key) * head_stride;   // from a key row to the value row of the same slot
 
   for (int k0 = k_begin + warp * KPW * UNROLL; k0 < k_end; k0 += DEC_WARPS * KPW * UNROLL) {
     uint4 kr[UNROLL], vr[UNROLL];
@@ -231,7 +232,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
       valid[u] = j < k_end;
       if (valid[u]) {
         const int page = tab[j / page_size];
-        const __nv_bfloat16* kp = pages + ((size_t)page * 2 * nkv + kvh) * head_stride + (size_t)(j % page_size) * D + chunk * 8;
+        const __nv_bfloat16* kp = pages + ((size_t)page * 2 * hm.n_stored + hm.key) * head_stride + (size_t)(j % page_size) * D + chunk * 8;
         kr[u] = ld_stream(kp);
         vr[u] = ld_stream(kp + v_off);
       } else {
@@ -365,7 +366,7 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const float* __restr
                        const float* __restrict__ sin_t, int rot, int write_kv, __nv_bfloat16* pages,
                        const int* __restrict__ items, int n_items, const int* __restrict__ positions,
                        const int* __restrict__ row_req, const int* __restrict__ table, int table_stride, int page_size,
-                       int nh, int nkv, float scale, float softcap, int window, int n_splits,
+                       int nh, int nkv, float scale, float softcap, int window, int vsplit, int n_splits,
                        float* __restrict__ partial, int* __restrict__ counters, __nv_bfloat16* __restrict__ out) {
   using namespace kf_mma;
   kf_pdl_trigger();
@@ -385,6 +386,7 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const float* __restr
   const int split = blockIdx.y;
   const int G = nh / nkv;
   const int h_first = kvh * G;
+  const KfHeadMap hm = kf_head_map(h_first, kvh, nh, nkv, vsplit);   // with the rotation inside (qkv given) vsplit is 0
   const int t = items ? items[item] : item;
   const int req = row_req[t];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -409,7 +411,7 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const float* __restr
 
   const int* tab = table + (size_t)req * table_stride;
   const size_t head_stride = (size_t)page_size * D;
-  const size_t v_off = (size_t)nkv * head_stride;
+  const size_t v_off = (size_t)(hm.n_stored + hm.value - hm.key) * head_stride;
   __nv_bfloat16* my = sKV + (size_t)warp * DM_BUFS * TILE;        // [buffer]
 
   // A warp walks its tiles (warp, warp + DM_WARPS, ...) as the sequence K0 V0 K1 V1 ...: item n is the keys (n even) or
@@ -426,7 +428,7 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const float* __restr
       const int j = j0 + lane;
       if (j < k_end) {
         const int page = tab[j / page_size];
-        if (page >= 0) row_base = ((long)page * 2 * nkv + kvh) * (long)head_stride + (long)(j % page_size) * D;
+        if (page >= 0) row_base = ((long)page * 2 * hm.n_stored + hm.key) * (long)head_stride + (long)(j % page_size) * D;
       }
     }
     __nv_bfloat16* dst = my + (size_t)buf * TILE;
@@ -494,7 +496,7 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const float* __restr
     for (int idx = tid; idx < 16 * CH; idx += blockDim.x) {
       const int r = idx / CH, c = idx - r * CH;
       uint4 v = make_uint4(0, 0, 0, 0);
-      if (r < G) v = *reinterpret_cast<const uint4*>(q + ((size_t)t * nh + h_first + r) * D + c * 8);
+      if (r < G) v = *reinterpret_cast<const uint4*>(q + ((size_t)t * hm.n_query + hm.query + r) * D + c * 8);
       *reinterpret_cast<uint4*>(tile_ptr<D>(sQ, r, c)) = v;
     }
   }
@@ -693,12 +695,12 @@ template <int D>
 int launch_decode_mma(const float* qkv, const float* cos_t, const float* sin_t, int rot, int write_kv,
                       const void* q, const void* pages, const int* items, int n_items, const int* positions,
                       const int* row_req, const int* table, int table_stride, int page_size, int nh, int nkv, float scale,
-                      float softcap, int window, int n_splits, float* partial, int* counters, void* out, cudaStream_t stream) {
+                      float softcap, int window, int vsplit, int n_splits, float* partial, int* counters, void* out, cudaStream_t stream) {
   const size_t smem = (size_t)(16 * D + DM_WARPS * DM_BUFS * DM_KEYS * D) * 2;
   if (decode_mma_blocks_per_sm<D>() < 1) return KF_ERR_SETUP;
   kf_launch(attn_decode_mma_kernel<D>, dim3(n_items * nkv, n_splits), dim3(DM_WARPS * 32), smem, stream,
             (const __nv_bfloat16*)q, qkv, cos_t, sin_t, rot, write_kv, (__nv_bfloat16*)const_cast<void*>(pages), items, n_items,
-            positions, row_req, table, table_stride, page_size, nh, nkv, scale, softcap, window, n_splits, partial, counters,
+            positions, row_req, table, table_stride, page_size, nh, nkv, scale, softcap, window, vsplit, n_splits, partial, counters,
             (__nv_bfloat16*)out);
   KF_CHECK_LAUNCH();
   return KF_OK;
@@ -707,12 +709,12 @@ int launch_decode_mma(const float* qkv, const float* cos_t, const float* sin_t, 
 template <int D, int HT>
 int launch_decode(const void* q, const void* pages, const int* items, int n_items, const int* positions, const int* row_req,
                   const int* table, int table_stride, int page_size, int nh, int nkv, float scale, float softcap, int window,
-                  int n_splits, float* partial, int* counters, void* out, cudaStream_t stream) {
+                  int vsplit, int n_splits, float* partial, int* counters, void* out, cudaStream_t stream) {
   const int G = nh / nkv;
   dim3 grid(n_items * nkv, n_splits, kf_ceil_div(G, HT));
   kf_launch(attn_decode_kernel<D, HT>, dim3(grid), dim3(DEC_WARPS * 32), 0, stream, 
       (const __nv_bfloat16*)q, (const __nv_bfloat16*)pages, items, n_items, positions, row_req, table, table_stride,
-      page_size, nh, nkv, scale, softcap, window, n_splits, partial, counters, (__nv_bfloat16*)out);
+      page_size, nh, nkv, scale, softcap, window, vsplit, n_splits, partial, counters, (__nv_bfloat16*)out);
   KF_CHECK_LAUNCH();
   return KF_OK;
 }
@@ -720,8 +722,8 @@ int launch_decode(const void* q, const void* pages, const int* items, int n_item
 template <int D>
 int launch_decode_d(int ht, const void* q, const void* pages, const int* items, int n_items, const int* positions,
                     const int* row_req, const int* table, int table_stride, int page_size, int nh, int nkv, float scale,
-                    float softcap, int window, int n_splits, float* partial, int* counters, void* out, cudaStream_t s) {
-#define KF_ARGS q, pages, items, n_items, positions, row_req, table, table_stride, page_size, nh, nkv, scale, softcap, window, n_splits, partial, counters, out, s
+                    float softcap, int window, int vsplit, int n_splits, float* partial, int* counters, void* out, cudaStream_t s) {
+#define KF_ARGS q, pages, items, n_items, positions, row_req, table, table_stride, page_size, nh, nkv, scale, softcap, window, vsplit, n_splits, partial, counters, out, s
   if (ht == 1) return launch_decode<D, 1>(KF_ARGS);
   if (ht == 2) return launch_decode<D, 2>(KF_ARGS);
   return launch_decode<D, 4>(KF_ARGS);
@@ -773,19 +775,19 @@ KF_API int kf_attention_decode_plan(int n_items, int nh, int nkv, int d, int max
   return KF_OK;
 }
 
-// q, out: [T, nh*d] bfloat16.  items: rows of the step this launch handles (null = rows 0..n_items-1).
+// q, out: [T, nh*d] bfloat16 (vsplit > 0: q has nh / vsplit heads, see KfHeadMap).  items: rows of the step this launch handles (null = rows 0..n_items-1).
 // partial: n_rows_total * nh * splits * (d + 4) floats; counters: n_items * nkv * ceil(G/ht) zeroed ints (left zero).
 KF_API int kf_attention_decode(const void* q, void* out, const void* pages, const int* items, int n_items,
                                const int* positions, const int* row_req, const int* table, int table_stride,
-                               int page_size, int nh, int nkv, int d, float scale, float softcap, int window, int ht,
-                               int n_splits, float* partial, int* counters, cudaStream_t stream) {
+                               int page_size, int nh, int nkv, int d, float scale, float softcap, int window, int vsplit,
+                               int ht, int n_splits, float* partial, int* counters, cudaStream_t stream) {
   if (n_items <= 0) return KF_OK;
-  if (nkv < 1 || nh % nkv != 0 || page_size < 1 || n_splits < 1) return KF_ERR_SIZE;
+  if (nkv < 1 || nh % nkv != 0 || page_size < 1 || n_splits < 1 || !kf_head_map_ok(nh, nkv, vsplit)) return KF_ERR_SIZE;
   if (n_splits > 1 && (!partial || !counters)) return KF_ERR_SIZE;
   if (n_splits > MERGE_MAX_SPLITS || ht > MERGE_MAX_HEADS) return KF_ERR_SIZE;
   if (ht == 0) {                                     // tensor-core variant
     if (nh / nkv > 16) return KF_ERR_SIZE;
-#define KF_MMA_ARGS nullptr, nullptr, nullptr, 0, 0, q, pages, items, n_items, positions, row_req, table, table_stride, page_size, nh, nkv, scale, softcap, window, n_splits, partial, counters, out, stream
+#define KF_MMA_ARGS nullptr, nullptr, nullptr, 0, 0, q, pages, items, n_items, positions, row_req, table, table_stride, page_size, nh, nkv, scale, softcap, window, vsplit, n_splits, partial, counters, out, stream
     switch (d) {
       case 16: return launch_decode_mma<16>(KF_MMA_ARGS);
       case 32: return launch_decode_mma<32>(KF_MMA_ARGS);
@@ -796,7 +798,7 @@ KF_API int kf_attention_decode(const void* q, void* out, const void* pages, cons
 #undef KF_MMA_ARGS
     return KF_ERR_SIZE;
   }
-#define KF_ARGS ht, q, pages, items, n_items, positions, row_req, table, table_stride, page_size, nh, nkv, scale, softcap, window, n_splits, partial, counters, out, stream
+#define KF_ARGS ht, q, pages, items, n_items, positions, row_req, table, table_stride, page_size, nh, nkv, scale, softcap, window, vsplit, n_splits, partial, counters, out, stream
   switch (d) {
     case 16: return launch_decode_d<16>(KF_ARGS);
     case 32: return launch_decode_d<32>(KF_ARGS);
@@ -821,7 +823,7 @@ KF_API int kf_attention_decode_fused(const float* qkv, const float* cos_t, const
   if (rot < 0 || rot > d || (rot & 1) || (rot > 0 && (!cos_t || !sin_t))) return KF_ERR_SIZE;
   if (n_splits > 1 && (!partial || !counters)) return KF_ERR_SIZE;
   if (n_splits > MERGE_MAX_SPLITS) return KF_ERR_SIZE;
-#define KF_MMA_ARGS qkv, cos_t, sin_t, rot, write_kv, nullptr, pages, items, n_items, positions, row_req, table, table_stride, page_size, nh, nkv, scale, softcap, window, n_splits, partial, counters, out, stream
+#define KF_MMA_ARGS qkv, cos_t, sin_t, rot, write_kv, nullptr, pages, items, n_items, positions, row_req, table, table_stride, page_size, nh, nkv, scale, softcap, window, 0, n_splits, partial, counters, out, stream
   switch (d) {
     case 16: return launch_decode_mma<16>(KF_MMA_ARGS);
     case 32: return launch_decode_mma<32>(KF_MMA_ARGS);
@@ -904,5 +906,5 @@ KF_API int kf_attention_decode_static(const void* q, void* out, const void* page
     }
   }
   return kf_attention_decode(q, out, pages, nullptr, n_rows, positions, row_req, table, table_stride, page_size, nh, nkv,
-                             d, scale, softcap, window, ht, splits, partial, counters, stream);
+                             d, scale, softcap, window, 0, ht, splits, partial, counters, stream);
 }

@@ -19,7 +19,7 @@ __global__ void __launch_bounds__(WARPS * 32)
 attention_generic_kernel(const TQ* __restrict__ q, TQ* __restrict__ out, const TKV* __restrict__ pages,
                          const int* __restrict__ items, const int* __restrict__ positions,
                          const int* __restrict__ row_req, const int* __restrict__ block_table, int table_stride,
-                         int page_size, int nh, int nkv, int d, float scale, float softcap, int window, int T) {
+                         int page_size, int nh, int nkv, int d, float scale, float softcap, int window, int vsplit, int T) {
   kf_pdl_trigger();
   kf_pdl_wait();
   __shared__ float qs[WARPS][MAX_D];
@@ -35,9 +35,10 @@ attention_generic_kernel(const TQ* __restrict__ q, TQ* __restrict__ out, const T
     return;
   }
   const int kvh = h / (nh / nkv);
+  const KfHeadMap hm = kf_head_map(h, kvh, nh, nkv, vsplit);
   const int pos = positions[t];
   const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
-  const TQ* qr = q + ((size_t)t * nh + h) * d;
+  const TQ* qr = q + ((size_t)t * hm.n_query + hm.query) * d;
   for (int i = lane; i < d; i += 32) qs[warp][i] = kf_load(qr, i);
   __syncwarp();
 
@@ -51,11 +52,11 @@ attention_generic_kernel(const TQ* __restrict__ q, TQ* __restrict__ out, const T
   for (int c0 = lo; c0 <= pos; c0 += 32) {
     const int j = c0 + lane;
     const bool valid = j <= pos;
-    long kofs = -1;                                         // element offset of key j's row; the value row is +nkv*head_stride
+    long kofs = -1;                                         // element offset of key j's row
     float s = -INFINITY;
     if (valid) {
       const int page = table[j / page_size];
-      kofs = (((long)page * 2) * nkv + kvh) * (long)head_stride + (long)(j % page_size) * d;
+      kofs = (((long)page * 2) * hm.n_stored + hm.key) * (long)head_stride + (long)(j % page_size) * d;
       const TKV* kr = pages + kofs;
       float dot = 0.f;
       for (int i = 0; i < d; ++i) dot = fmaf(qs[warp][i], kf_load(kr, i), dot);
@@ -70,7 +71,7 @@ attention_generic_kernel(const TQ* __restrict__ q, TQ* __restrict__ out, const T
     const int n = min(32, pos - c0 + 1);
     for (int u = 0; u < n; ++u) {
       const float pu = __shfl_sync(0xffffffffu, p, u);
-      const long vofs = __shfl_sync(0xffffffffu, kofs, u) + (long)nkv * (long)head_stride;
+      const long vofs = __shfl_sync(0xffffffffu, kofs, u) + (long)(hm.n_stored + hm.value - hm.key) * (long)head_stride;
       const TKV* vr = pages + vofs;
 #pragma unroll
       for (int r = 0; r < MAX_D / 32; ++r) {
@@ -92,15 +93,15 @@ attention_generic_kernel(const TQ* __restrict__ q, TQ* __restrict__ out, const T
 KF_API int kf_attention_generic(const void* q, void* out, int q_dtype, const void* pages, int kv_dtype,
                                 const int* items, const int* positions, const int* row_req, const int* block_table, int table_stride,
                                 int page_size, int nh, int nkv, int d, float scale, float softcap, int window,
-                                int T, cudaStream_t stream) {
+                                int vsplit, int T, cudaStream_t stream) {
   if (T <= 0) return KF_OK;
-  if (d < 1 || d > MAX_D || nkv < 1 || nh % nkv != 0 || page_size < 1) return KF_ERR_SIZE;
+  if (d < 1 || d > MAX_D || nkv < 1 || nh % nkv != 0 || page_size < 1 || !kf_head_map_ok(nh, nkv, vsplit)) return KF_ERR_SIZE;
   const long n_work = (long)T * nh;
   const int blocks = (int)((n_work + WARPS - 1) / WARPS);
 #define KF_GO(TQ, TKV)                                                                                     \
   kf_launch(attention_generic_kernel<TQ, TKV>, dim3(blocks), dim3(WARPS * 32), 0, stream,                                     \
       (const TQ*)q, (TQ*)out, (const TKV*)pages, items, positions, row_req, block_table, table_stride, page_size, \
-      nh, nkv, d, scale, softcap, window, T)
+      nh, nkv, d, scale, softcap, window, vsplit, T)
   if (q_dtype == KF_F32 && kv_dtype == KF_F32) KF_GO(float, float);
   else if (q_dtype == KF_BF16 && kv_dtype == KF_BF16) KF_GO(__nv_bfloat16, __nv_bfloat16);
   else return KF_ERR_DTYPE;

@@ -27,7 +27,7 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
                     const int* __restrict__ tile_row0, const int* __restrict__ tile_nrows,
                     const int* __restrict__ positions, const int* __restrict__ row_req,
                     const int* __restrict__ table, int table_stride, int page_size, int nh, int nkv,
-                    float scale, float softcap, int window, __nv_bfloat16* __restrict__ out) {
+                    float scale, float softcap, int window, int vsplit, __nv_bfloat16* __restrict__ out) {
   kf_pdl_trigger();
   kf_pdl_wait();
   constexpr int CH = D / 8;                       // 16-byte chunks per row
@@ -45,6 +45,7 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
   const int req = row_req[row0];
   if (req < 0 || nrows <= 0) return;                          // padding, or a tile without rows
   const int kvh = h / (nh / nkv);
+  const KfHeadMap hm = kf_head_map(h, kvh, nh, nkv, vsplit);
   const int pos0 = positions[row0];                               // rows of a request are consecutive positions
   const int pos_last = pos0 + nrows - 1;
   const int lo = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;
@@ -54,13 +55,13 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
   const int g = lane >> 2, tq = lane & 3;
   const int* tab = table + (size_t)req * table_stride;
   const size_t head_stride = (size_t)page_size * D;
-  const size_t v_off = (size_t)nkv * head_stride;
+  const size_t v_off = (size_t)(hm.n_stored + hm.value - hm.key) * head_stride;   // from a key row to the value row of the same slot
 
   // ---- Q tile -> shared (rows past the tile are zero) -------------------------------------------------------
   for (int idx = tid; idx < BM * CH; idx += PF_WARPS * 32) {
     const int r = idx / CH, c = idx - r * CH;
     const bool ok = r < nrows;
-    const __nv_bfloat16* src = q + ((size_t)(row0 + (ok ? r : 0)) * nh + h) * D + c * 8;
+    const __nv_bfloat16* src = q + ((size_t)(row0 + (ok ? r : 0)) * hm.n_query + hm.query) * D + c * 8;
     cp_async16(tile_ptr<D>(sQ, r, c), src, ok);
   }
   auto load_kv = [&](int kt, int stage) {
@@ -72,7 +73,7 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
       bool ok = j <= pos_last;
       int page = 0;
       if (ok) { page = tab[j / page_size]; ok = page >= 0; }
-      const __nv_bfloat16* src = pages + ((size_t)(ok ? page : 0) * 2 * nkv + kvh) * head_stride +
+      const __nv_bfloat16* src = pages + ((size_t)(ok ? page : 0) * 2 * hm.n_stored + hm.key) * head_stride +
                                  (size_t)(ok ? j % page_size : 0) * D + c * 8;
       cp_async16(tile_ptr<D>(dk, r, c), src, ok);
       cp_async16(tile_ptr<D>(dv, r, c), src + v_off, ok);
@@ -203,7 +204,7 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
 template <int D, int BNK>
 int launch_prefill(const void* q, void* out, const void* pages, const int* tile_row0, const int* tile_nrows, int n_tiles,
                    const int* positions, const int* row_req, const int* table, int table_stride, int page_size,
-                   int nh, int nkv, float scale, float softcap, int window, cudaStream_t stream) {
+                   int nh, int nkv, float scale, float softcap, int window, int vsplit, cudaStream_t stream) {
   const size_t smem = (size_t)(BM * D + 4 * BNK * D) * 2;
   static bool configured = false;
   if (!configured) {
@@ -215,7 +216,7 @@ int launch_prefill(const void* q, void* out, const void* pages, const int* tile_
   }
   kf_launch(attn_prefill_kernel<D, BNK>, dim3(n_tiles, nh), dim3(PF_WARPS * 32), smem, stream, 
       (const __nv_bfloat16*)q, (const __nv_bfloat16*)pages, tile_row0, tile_nrows, positions, row_req, table, table_stride,
-      page_size, nh, nkv, scale, softcap, window, (__nv_bfloat16*)out);
+      page_size, nh, nkv, scale, softcap, window, vsplit, (__nv_bfloat16*)out);
   KF_CHECK_LAUNCH();
   return KF_OK;
 }
@@ -229,11 +230,11 @@ KF_API int kf_attention_prefill_tile_rows() { return BM; }
 // a tile belong to one request and hold consecutive positions.
 KF_API int kf_attention_prefill(const void* q, void* out, const void* pages, const int* tile_row0, const int* tile_nrows,
                                 int n_tiles, const int* positions, const int* row_req, const int* table, int table_stride,
-                                int page_size, int nh, int nkv, int d, float scale, float softcap, int window,
+                                int page_size, int nh, int nkv, int d, float scale, float softcap, int window, int vsplit,
                                 cudaStream_t stream) {
   if (n_tiles <= 0) return KF_OK;
-  if (nkv < 1 || nh % nkv != 0 || page_size < 1) return KF_ERR_SIZE;
-#define KF_ARGS q, out, pages, tile_row0, tile_nrows, n_tiles, positions, row_req, table, table_stride, page_size, nh, nkv, scale, softcap, window, stream
+  if (nkv < 1 || nh % nkv != 0 || page_size < 1 || !kf_head_map_ok(nh, nkv, vsplit)) return KF_ERR_SIZE;
+#define KF_ARGS q, out, pages, tile_row0, tile_nrows, n_tiles, positions, row_req, table, table_stride, page_size, nh, nkv, scale, softcap, window, vsplit, stream
   switch (d) {
     case 16: return launch_prefill<16, 64>(KF_ARGS);
     case 32: return launch_prefill<32, 64>(KF_ARGS);

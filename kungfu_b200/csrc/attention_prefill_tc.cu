@@ -207,7 +207,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
                        const int* __restrict__ tile_row0, const int* __restrict__ tile_nrows,
                        const int* __restrict__ positions, const int* __restrict__ row_req,
                        const int* __restrict__ table, int table_stride, int page_size, int nh, int nkv,
-                       float scale, float softcap, int window, __nv_bfloat16* __restrict__ out,
+                       float scale, float softcap, int window, int vsplit, __nv_bfloat16* __restrict__ out,
                        int* __restrict__ error_flag, int n_parts, int run_tiles, float* __restrict__ partial) {
   constexpr int NSUB = D / 64;                            // 64-element sub-tiles along the head dimension
   constexpr int Q_BYTES = BMQ * D * 2;
@@ -248,6 +248,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
   const int tile = (int)(gridDim.x / (nh * n_parts)) - 1 - slot / n_parts, part = slot % n_parts;
   const int row0 = tile_row0[tile], nrows = tile_nrows[tile];
   const int kvh = h / (nh / nkv);
+  const KfHeadMap hm = kf_head_map(h, kvh, nh, nkv, vsplit);
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
@@ -294,14 +295,14 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_kv) : "memory");
       mbar_expect_tx(q_full, Q_BYTES);
 #pragma unroll
-      for (int j = 0; j < NSUB; ++j) tma_load_2d(sQ + j * (BMQ * 128), &tm_q, q_full, h * D + j * 64, row0);
+      for (int j = 0; j < NSUB; ++j) tma_load_2d(sQ + j * (BMQ * 128), &tm_q, q_full, hm.query * D + j * 64, row0);
       const int* tab = table + (size_t)req * table_stride;
       for (int i = 0; i < n_tiles; ++i) {
         const int s = i & 1;
         const int kt = kt_begin + i * BKV;
         int page = tab[kt / page_size];
         if (page < 0) page = 0;                            // a page already given back: every key of it is masked
-        const int krow = ((page * 2 + 0) * nkv + kvh) * page_size + (kt % page_size);
+        const int krow = ((page * 2 + 0) * hm.n_stored + hm.key) * page_size + (kt % page_size);
         if (i >= 2 && !mbar_wait(&k_free[s], ((i >> 1) - 1) & 1)) { atomicExch(error_flag, ERR_ATTN_WAIT + 1); *s_abort = 1; break; }
         mbar_expect_tx(&k_full[s], KV_BYTES);
 #pragma unroll
@@ -317,7 +318,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         const int kt = kt_begin + i * BKV;
         int page = tab[kt / page_size];
         if (page < 0) page = 0;
-        const int vrow = ((page * 2 + 1) * nkv + kvh) * page_size + (kt % page_size);
+        const int vrow = ((page * 2 + 1) * hm.n_stored + hm.value) * page_size + (kt % page_size);
         if (i >= 2 && !mbar_wait(&v_free[s], ((i >> 1) - 1) & 1)) { atomicExch(error_flag, ERR_ATTN_WAIT + 1); *s_abort = 1; break; }
         mbar_expect_tx(&v_full[s], KV_BYTES);
 #pragma unroll
@@ -637,7 +638,7 @@ bool tensor_map(const void* base, long rows, long cols, int box_rows, CUtensorMa
 template <int D>
 int launch(const CUtensorMap& tq, const CUtensorMap& tkv, const int* tile_row0, const int* tile_nrows, int n_tiles,
            const int* positions, const int* row_req, const int* table, int table_stride, int page_size, int nh, int nkv,
-           float scale, float softcap, int window, void* out, int* error_flag, int n_parts, int run_tiles,
+           float scale, float softcap, int window, int vsplit, void* out, int* error_flag, int n_parts, int run_tiles,
            float* partial, cudaStream_t stream) {
   const size_t smem = (size_t)BMQ * D * 2 + 4 * (size_t)BKV * D * 2 + (size_t)BMQ * BKV * 2 + 1024 + 256 + 4 * BMQ * 4;
   static bool configured = false;
@@ -649,7 +650,7 @@ int launch(const CUtensorMap& tq, const CUtensorMap& tkv, const int* tile_row0, 
     configured = true;
   }
   kf_launch(attn_prefill_tc_kernel<D>, dim3(n_tiles * n_parts * nh), dim3(THREADS), smem, stream, tq, tkv, tile_row0, tile_nrows,
-            positions, row_req, table, table_stride, page_size, nh, nkv, scale, softcap, window, (__nv_bfloat16*)out,
+            positions, row_req, table, table_stride, page_size, nh, nkv, scale, softcap, window, vsplit, (__nv_bfloat16*)out,
             error_flag, n_parts, run_tiles, partial);
   KF_CHECK_LAUNCH();
   if (n_parts > 1) {
@@ -711,15 +712,16 @@ KF_API int kf_attention_prefill_tc_plan(int n_tiles, int nh, int max_keys, int* 
 KF_API int kf_attention_prefill_tc(const void* q, void* out, const void* pages, long n_pages, int T, const int* tile_row0,
                                    const int* tile_nrows, int n_tiles, const int* positions, const int* row_req,
                                    const int* table, int table_stride, int page_size, int nh, int nkv, int d, float scale,
-                                   float softcap, int window, int* error_flag, int n_parts, int run_tiles, float* partial,
-                                   cudaStream_t stream) {
+                                   float softcap, int window, int vsplit, int* error_flag, int n_parts, int run_tiles,
+                                   float* partial, cudaStream_t stream) {
   if (n_tiles <= 0) return KF_OK;
-  if (nkv < 1 || nh % nkv != 0 || page_size % 64 != 0) return KF_ERR_SIZE;
+  if (nkv < 1 || nh % nkv != 0 || page_size % 64 != 0 || !kf_head_map_ok(nh, nkv, vsplit)) return KF_ERR_SIZE;
+  const KfHeadMap hm = kf_head_map(0, 0, nh, nkv, vsplit);
   if (n_parts < 1 || n_parts > 8 || (n_parts > 1 && !partial) || run_tiles < 0) return KF_ERR_SIZE;
   CUtensorMap tq, tkv;
-  if (!tensor_map(q, T, (long)nh * d, BMQ, &tq)) return KF_ERR_SETUP;
-  if (!tensor_map(pages, n_pages * 2 * nkv * page_size, d, BKV, &tkv)) return KF_ERR_SETUP;
-#define KF_ARGS tq, tkv, tile_row0, tile_nrows, n_tiles, positions, row_req, table, table_stride, page_size, nh, nkv, scale, softcap, window, out, error_flag, n_parts, run_tiles, partial, stream
+  if (!tensor_map(q, T, (long)hm.n_query * d, BMQ, &tq)) return KF_ERR_SETUP;
+  if (!tensor_map(pages, n_pages * 2 * hm.n_stored * page_size, d, BKV, &tkv)) return KF_ERR_SETUP;
+#define KF_ARGS tq, tkv, tile_row0, tile_nrows, n_tiles, positions, row_req, table, table_stride, page_size, nh, nkv, scale, softcap, window, vsplit, out, error_flag, n_parts, run_tiles, partial, stream
   switch (d) {
     case 64: return launch<64>(KF_ARGS);
     case 128: return launch<128>(KF_ARGS);

@@ -122,3 +122,34 @@ __device__ __forceinline__ float kf_clamped_swish(float g, float u, float limit)
 __device__ __forceinline__ float kf_softcap(float x, float cap) { return cap > 0.f ? cap * tanhf(x / cap) : x; }
 
 static inline int kf_ceil_div(long a, long b) { return (int)((a + b - 1) / b); }
+
+// Which stored heads an attention head reads.  Ordinarily (vsplit = 0) the nh heads of a row of q and of the result are
+// the same, and head h reads the keys and the values of stored head h / (nh / nkv).
+// vsplit = G > 0 ("every query head over every value head"): the result has nh heads, the pages hold nkv / G heads of keys
+// and as many of values, and a row of q holds nh / G heads.  Result head h belongs to the pair p = h / (nh / nkv) of a key
+// head p / G and a value head p % G; it is the attention of query head (p / G) * (nh / nkv) + h % (nh / nkv) over that key
+// head's keys and that value head's values.  nkv must be G * G then.
+struct KfHeadMap {
+  int query, n_query;      // the head of q this result head reads, and how many heads a row of q has
+  int key, value;          // the stored heads whose keys and whose values it reads
+  int n_stored;            // heads per page (of keys; as many of values)
+};
+
+__host__ __device__ __forceinline__ KfHeadMap kf_head_map(int h, int kvh, int nh, int nkv, int vsplit) {
+  KfHeadMap m;
+  if (vsplit > 0) {
+    const int per = nh / nkv;
+    m.key = kvh / vsplit;
+    m.value = kvh - m.key * vsplit;
+    m.query = m.key * per + h % per;
+    m.n_query = nh / vsplit;
+    m.n_stored = nkv / vsplit;
+  } else {
+    m.query = h, m.n_query = nh, m.key = m.value = kvh, m.n_stored = nkv;
+  }
+  return m;
+}
+
+static inline bool kf_head_map_ok(int nh, int nkv, int vsplit) {
+  return vsplit == 0 || (vsplit > 0 && nkv == vsplit * vsplit && nh % nkv == 0);
+}

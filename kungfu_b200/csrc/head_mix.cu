@@ -6,18 +6,17 @@
 //   b_h(i, j) = sum_g M[h, g] a_g(i, j)                                       (mixed weights)
 //   out_h(i)  = sum_j b_h(i, j) v_(h / r)(j)  =  sum_g M[h, g] * O[g, h / r](i),   O[g, c] = sum_j a_g(., j) v_c(j).
 // O[g, c] is plain attention of query head g over the keys of its own key head and the values of value head c, so the
-// attention kernels run H * G "wide" heads over G * G wide key/value heads: wide key/value head (ck, cv) holds the keys
-// of head ck and the values of head cv, and wide query head ((ck * G + cv) * r + i) is query head g = ck * r + i.
+// attention kernels produce H * G result heads from H query heads and G stored heads (their `vsplit` = G, see KfHeadMap):
+// result head ((ck * G + cv) * r + i) is query head g = ck * r + i over the values of head cv.
 //
-// kf_rotate_norm_append: from the 32-bit q|k|v projection to those operands.  Per head of q and k: the first `rot`
-//   elements are turned in pairs (i, i + rot/2) by the step's cos/sin table times `mag`, then (when `unit_norm`) the head
-//   is divided by sqrt(mean(head^2) + eps); v passes as it is.  q goes to its G wide query heads, k to the wide heads
-//   (ck, *), v to the wide heads (*, cv), at the token's place in the request's pages.  With wide = 0 nothing is
-//   repeated (G plain key/value heads).  Heads use D elements in q and pages, tails zero.
+// kf_rotate_norm_append: from the 32-bit q|k|v projection to the attention's operands.  Per head of q and k: the first
+//   `rot` elements are turned in pairs (i, i + rot/2) by the step's cos/sin table times `mag`, then (when `unit_norm`) the
+//   head is divided by sqrt(mean(head^2) + eps); v passes as it is.  q goes to q_out, k and v to the token's place in the
+//   request's pages.  Heads use D elements in q and pages, tails zero.
 // kf_head_mix_gate: out[t, h * dv + e] = gate(t, h * dv + e) * sum_g M[h, g] * o[t, wide(g, h / r), e], sums in 32-bit in
 //   ascending g, gate = sigmoid of a column range of a 32-bit matrix (null: no gate).  Without M (null) it is the gate
 //   and the packing alone.
-// One warp per (row, head); everything is computed in 32-bit, only the stores round.
+// Everything is computed in 32-bit, only the stores round.
 #include "common.cuh"
 
 constexpr int HM_MAX_D = 256;
@@ -27,7 +26,7 @@ template <typename TQ, typename TKV>
 __global__ void __launch_bounds__(HM_WARPS * 32)
 rotate_norm_append_kernel(const float* __restrict__ in, int ld, int col0, const float* __restrict__ cos_t,
                           const float* __restrict__ sin_t, int rot, float mag, int unit_norm, float eps, int nh, int nkv,
-                          int dk, int dv, int D, int wide, const int* __restrict__ positions,
+                          int dk, int dv, int D, const int* __restrict__ positions,
                           const int* __restrict__ row_req, const int* __restrict__ block_table, int table_stride,
                           int page_size, TKV* __restrict__ pages, TQ* __restrict__ q_out, int write_kv, int T) {
   kf_pdl_trigger();
@@ -41,15 +40,9 @@ rotate_norm_append_kernel(const float* __restrict__ in, int ld, int col0, const 
   const int req = row_req[t];
   const int kind = hslot < nh ? 0 : (hslot < nh + nkv ? 1 : 2);            // query, key, value
   const int head = kind == 0 ? hslot : (kind == 1 ? hslot - nh : hslot - nh - nkv);
-  const int reps = wide ? nkv : 1;
-  const int per = nh / nkv;
-  const int nq = nh * reps, nst = nkv * reps;               // query heads and stored key/value heads as the attention sees them
   if (req < 0) {                                            // padding row: zero queries, nothing filed
     if (kind == 0)
-      for (int c = 0; c < reps; ++c) {
-        const int wq = wide ? ((head / per) * nkv + c) * per + head % per : head;
-        for (int i = lane; i < D; i += 32) kf_store(q_out, ((size_t)t * nq + wq) * D + i, 0.f);
-      }
+      for (int i = lane; i < D; i += 32) kf_store(q_out, ((size_t)t * nh + head) * D + i, 0.f);
     return;
   }
   if (kind != 0 && !write_kv) return;
@@ -89,29 +82,25 @@ rotate_norm_append_kernel(const float* __restrict__ in, int ld, int col0, const 
     in_page = pos % page_size;
     if (page < 0) return;                                   // never for a reserved position; guards the store
   }
-  for (int c = 0; c < reps; ++c) {
-    if (kind == 0) {
-      const int wq = wide ? ((head / per) * nkv + c) * per + head % per : head;
-      TQ* o = q_out + ((size_t)t * nq + wq) * D;
+  if (kind == 0) {
+    TQ* o = q_out + ((size_t)t * nh + head) * D;
 #pragma unroll
-      for (int k = 0; k < HM_MAX_D / 32; ++k) {
-        const int i = lane + 32 * k;
-        if (i < D) kf_store(o, i, v[k]);
-      }
-    } else {
-      const int st = wide ? (kind == 1 ? head * nkv + c : c * nkv + head) : head;
-      TKV* o = pages + ((((size_t)page * 2 + (kind - 1)) * nst + st) * page_size + in_page) * D;
+    for (int k = 0; k < HM_MAX_D / 32; ++k) {
+      const int i = lane + 32 * k;
+      if (i < D) kf_store(o, i, v[k]);
+    }
+  } else {
+    TKV* o = pages + ((((size_t)page * 2 + (kind - 1)) * nkv + head) * page_size + in_page) * D;
 #pragma unroll
-      for (int k = 0; k < HM_MAX_D / 32; ++k) {
-        const int i = lane + 32 * k;
-        if (i < D) kf_store(o, i, v[k]);
-      }
+    for (int k = 0; k < HM_MAX_D / 32; ++k) {
+      const int i = lane + 32 * k;
+      if (i < D) kf_store(o, i, v[k]);
     }
   }
 }
 
 KF_API int kf_rotate_norm_append(const float* in, int ld, int col0, const float* cos_t, const float* sin_t, int rot, float mag,
-                                 int unit_norm, float eps, int nh, int nkv, int dk, int dv, int D, int wide,
+                                 int unit_norm, float eps, int nh, int nkv, int dk, int dv, int D,
                                  const int* positions, const int* row_req, const int* block_table, int table_stride,
                                  int page_size, void* pages, int kv_dtype, void* q_out, int q_dtype, int write_kv, int T,
                                  cudaStream_t stream) {
@@ -122,7 +111,7 @@ KF_API int kf_rotate_norm_append(const float* in, int ld, int col0, const float*
   const dim3 grid((unsigned)((n_work + HM_WARPS - 1) / HM_WARPS));
 #define KF_GO(TQ, TKV)                                                                                                   \
   kf_launch(rotate_norm_append_kernel<TQ, TKV>, grid, dim3(HM_WARPS * 32), 0, stream, in, ld, col0, cos_t, sin_t, rot, mag, \
-            unit_norm, eps, nh, nkv, dk, dv, D, wide, positions, row_req, block_table, table_stride, page_size,           \
+            unit_norm, eps, nh, nkv, dk, dv, D, positions, row_req, block_table, table_stride, page_size,           \
             (TKV*)pages, (TQ*)q_out, write_kv, T)
   if (q_dtype == KF_F32 && kv_dtype == KF_F32) KF_GO(float, float);
   else if (q_dtype == KF_BF16 && kv_dtype == KF_BF16) KF_GO(__nv_bfloat16, __nv_bfloat16);
@@ -132,48 +121,93 @@ KF_API int kf_rotate_norm_append(const float* in, int ld, int col0, const float*
   return KF_OK;
 }
 
+constexpr int HG_THREADS = 128;
+constexpr int HG_HEADS = 8;                                 // result heads a thread sums at a time
+
+__device__ __forceinline__ float2 hg_load2(const float* p) { return *reinterpret_cast<const float2*>(p); }
+__device__ __forceinline__ float2 hg_load2(const __nv_bfloat16* p) {
+  return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p));
+}
+
+// One thread per (row, value head c, pair of elements): it reads the pair of every query head's result over value head c
+// once and sums it into the r heads of c's group.  M sits in shared memory when it fits (else it is read through L1).
 template <typename TQ, typename TW>
-__global__ void head_mix_gate_kernel(const TQ* __restrict__ o, const TW* __restrict__ mix, const float* __restrict__ g, int ld,
-                                     int gcol0, int nh, int nkv, int dv, int D, TQ* __restrict__ out,
-                                     const int* __restrict__ row_req) {
+__global__ void __launch_bounds__(HG_THREADS)
+head_mix_gate_kernel(const TQ* __restrict__ o, const TW* __restrict__ mix, const float* __restrict__ g, int ld, int gcol0,
+                     int nh, int nkv, int dv, int D, TQ* __restrict__ out, const int* __restrict__ row_req, int T,
+                     int mix_in_smem) {
   kf_pdl_trigger();
   kf_pdl_wait();
   extern __shared__ float ms[];                             // the mixing matrix [nh, nh]
-  if (mix)
+  if (mix && mix_in_smem) {
     for (int i = threadIdx.x; i < nh * nh; i += blockDim.x) ms[i] = kf_load(mix, i);
-  __syncthreads();
-  const int t = blockIdx.x;
-  const bool pad = row_req[t] < 0;
+    __syncthreads();
+  }
   const int per = nh / nkv;
-  const int nq = mix ? nh * nkv : nh;
-  for (int e = threadIdx.x; e < nh * dv; e += blockDim.x) {
-    const int h = e / dv, i = e - h * dv;
-    float v = 0.f;
-    if (!pad) {
-      if (mix) {
-        const int cv = h / per;
-        for (int gq = 0; gq < nh; ++gq) {
-          const int wq = ((gq / per) * nkv + cv) * per + gq % per;
-          v = fmaf(ms[h * nh + gq], kf_load(o, ((size_t)t * nq + wq) * D + i), v);
-        }
-      } else {
-        v = kf_load(o, ((size_t)t * nq + h) * D + i);
-      }
-      if (g) v *= 1.f / (1.f + expf(-g[(size_t)t * ld + gcol0 + e]));
+  const int pairs = (dv + 1) >> 1;
+  const int groups = mix ? nkv : nh;                        // without M every head is a group of its own
+  const long item = (long)blockIdx.x * HG_THREADS + threadIdx.x;
+  if (item >= (long)T * groups * pairs) return;
+  const int ip = (int)(item % pairs);
+  const int cv = (int)((item / pairs) % groups);
+  const int t = (int)(item / ((long)pairs * groups));
+  const int i = 2 * ip;
+  const bool two = i + 1 < dv;
+  const bool pad = row_req[t] < 0;
+  auto put = [&](int h, float a, float b) {
+    const size_t e = (size_t)h * dv + i;
+    if (pad) a = b = 0.f;
+    else if (g) {
+      const float* gr = g + (size_t)t * ld + gcol0 + e;
+      a *= 1.f / (1.f + expf(-gr[0]));
+      if (two) b *= 1.f / (1.f + expf(-gr[1]));
     }
-    kf_store(out, (size_t)t * nh * dv + e, v);
+    kf_store(out, (size_t)t * nh * dv + e, a);
+    if (two) kf_store(out, (size_t)t * nh * dv + e + 1, b);
+  };
+  if (!mix) {
+    const float2 v = pad ? make_float2(0.f, 0.f) : hg_load2(o + ((size_t)t * nh + cv) * D + i);
+    put(cv, v.x, v.y);
+    return;
+  }
+  const TQ* orow = o + (size_t)t * nh * nkv * D + i;
+  for (int h0 = 0; h0 < per; h0 += HG_HEADS) {
+    float ax[HG_HEADS], ay[HG_HEADS];
+#pragma unroll
+    for (int j = 0; j < HG_HEADS; ++j) ax[j] = ay[j] = 0.f;
+    if (!pad) {
+      for (int gq = 0; gq < nh; ++gq) {
+        const int wq = ((gq / per) * nkv + cv) * per + gq % per;
+        const float2 v = hg_load2(orow + (size_t)wq * D);
+#pragma unroll
+        for (int j = 0; j < HG_HEADS; ++j) {
+          if (h0 + j < per) {
+            const int mi = (cv * per + h0 + j) * nh + gq;
+            const float m = mix_in_smem ? ms[mi] : kf_load(mix, mi);
+            ax[j] = fmaf(m, v.x, ax[j]);
+            ay[j] = fmaf(m, v.y, ay[j]);
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < HG_HEADS; ++j)
+      if (h0 + j < per) put(cv * per + h0 + j, ax[j], ay[j]);
   }
 }
 
 KF_API int kf_head_mix_gate(const void* o, const void* mix, int w_dtype, const float* g, int ld, int gcol0, int nh, int nkv,
                             int dv, int D, void* out, int dtype, const int* row_req, int T, cudaStream_t stream) {
   if (T <= 0) return KF_OK;
-  if (nkv < 1 || nh % nkv || dv > D || nh > 128) return KF_ERR_SIZE;
-  const int threads = nh * dv >= 1024 ? 256 : 128;
-  const size_t smem = mix ? (size_t)nh * nh * sizeof(float) : 0;
+  if (nkv < 1 || nh % nkv || dv > D || (D & 1)) return KF_ERR_SIZE;
+  const size_t want = mix ? (size_t)nh * nh * sizeof(float) : 0;
+  const int in_smem = want <= 40 * 1024;
+  const size_t smem = in_smem ? want : 0;
+  const long n_work = (long)T * (mix ? nkv : nh) * ((dv + 1) / 2);
+  const dim3 grid((unsigned)((n_work + HG_THREADS - 1) / HG_THREADS));
 #define KF_GO(TQ, TW)                                                                                                \
-  kf_launch(head_mix_gate_kernel<TQ, TW>, dim3(T), dim3(threads), smem, stream, (const TQ*)o, (const TW*)mix, g, ld, gcol0, \
-            nh, nkv, dv, D, (TQ*)out, row_req)
+  kf_launch(head_mix_gate_kernel<TQ, TW>, grid, dim3(HG_THREADS), smem, stream, (const TQ*)o, (const TW*)mix, g, ld, gcol0, \
+            nh, nkv, dv, D, (TQ*)out, row_req, T, in_smem)
   if (dtype == KF_F32 && w_dtype == KF_F32) KF_GO(float, float);
   else if (dtype == KF_BF16 && w_dtype == KF_BF16) KF_GO(__nv_bfloat16, __nv_bfloat16);
   else if (dtype == KF_BF16 && w_dtype == KF_F32) KF_GO(__nv_bfloat16, float);

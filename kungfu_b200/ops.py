@@ -463,16 +463,19 @@ def linear_rope_kv_append(x, wqkv, cos, sin, rot: int, n_heads: int, n_kv_heads:
 
 @_dispatch("paged_attention")
 def paged_attention(q, out, ctx, cache, n_heads: int, n_kv_heads: int, head_dim: int, scale: float, softcap: float,
-                    window: int | None) -> None:
+                    window: int | None, value_split: int = 0) -> None:
     """Causal (optionally windowed, softcapped) attention of every row of the step over its request's pages.
     bfloat16: rows of single-row requests run the split-KV decode kernel, the rest the prefill kernel, when the
-    head size has an instance of them; the 32-bit path and other head sizes run the generic kernel."""
+    head size has an instance of them; the 32-bit path and other head sizes run the generic kernel.
+    value_split = G > 0: every query head over every value head.  `out` has n_heads result heads, q n_heads / G heads and
+    the pages G heads (n_kv_heads = G * G counts (key head, value head) pairs): result head h, of pair p = h // r with
+    r = n_heads // n_kv_heads, is query head (p // G) * r + h % r over the keys of head p // G and the values of head p % G."""
     T = q.shape[0]
     lib = library()
     table = ctx.block_tables[cache.group]
     pages = cache.pages
     common = (_p(ctx.positions), _p(ctx.row_req), _p(table), table.shape[1], cache.page_size, n_heads, n_kv_heads, head_dim,
-              _f(scale), _f(softcap), int(window or 0))
+              _f(scale), _f(softcap), int(window or 0), int(value_split))
     n_dec = getattr(ctx, "n_dec_rows", 0)
     fast = (use_fast_attention and q.dtype == torch.bfloat16 and pages.dtype == torch.bfloat16)
     if fast and n_dec > 0 and lib.kf_attention_decode_supported(head_dim):
@@ -491,7 +494,7 @@ def paged_attention(q, out, ctx, cache, n_heads: int, n_kv_heads: int, head_dim:
         else:
             partial = _partial(q.device, T * n_heads * splits.value * (head_dim + 4)) if splits.value > 1 else None
             items = None if n_dec == T else ctx.dec_rows
-            _check(lib.kf_attention_decode(_p(q), _p(out), _p(pages), _p(items), n_dec, *common[:8], *common[8:], ht.value,
+            _check(lib.kf_attention_decode(_p(q), _p(out), _p(pages), _p(items), n_dec, *common, ht.value,
                                            splits.value, _p(partial), _p(sc["counters"]), _stream()), "attention (decode)")
             if n_dec == T:
                 return
@@ -723,21 +726,18 @@ def poly_norm(z, coef, eps: float, out) -> None:
 
 @_dispatch("rotate_norm_append")
 def rotate_norm_append(proj, col0: int, cos, sin, rot: int, magnitude: float, unit_norm: bool, eps: float, n_heads: int,
-                       n_kv_heads: int, key_dim: int, value_dim: int, wide: bool, ctx, cache, q_out) -> None:
+                       n_kv_heads: int, key_dim: int, value_dim: int, ctx, cache, q_out) -> None:
     """From the 32-bit q|k|v projection (columns col0.. of proj) to the attention's operands: q and k turned in pairs
     (i, i + rot/2) by cos/sin * magnitude, then (unit_norm) divided by sqrt(mean(head^2) + eps); q into q_out, k and v
-    into the pages of `cache`, heads of D = the pages' head size with zero tails.  `wide`: every query head is stored
-    once per value head and the pages hold n_kv_heads^2 heads, (key head, value head) pairs, so that the attention
-    kernels give every query head's weighted sum over every value head (see `head_mix_gate`)."""
+    into the pages of `cache`, heads of D = the pages' head size with zero tails."""
     T = q_out.shape[0]
     D = cache.pages.shape[-1]
-    reps = n_kv_heads if wide else 1
-    if q_out.shape[1] != n_heads * reps * D or cache.pages.shape[2] != n_kv_heads * reps:
+    if q_out.shape[1] != n_heads * D or cache.pages.shape[2] != n_kv_heads:
         raise KernelError(f"rotate_norm_append: q rows of {q_out.shape[1]} and pages of {cache.pages.shape[2]} heads do not fit "
-                          f"{n_heads} x {reps} query heads and {n_kv_heads} x {reps} stored heads of {D}")
+                          f"{n_heads} query heads and {n_kv_heads} stored heads of {D}")
     table = ctx.block_tables[cache.group]
     _check(library().kf_rotate_norm_append(_p(proj), proj.shape[1], int(col0), _p(cos), _p(sin), int(rot), _f(magnitude),
-                                           int(bool(unit_norm)), _f(eps), n_heads, n_kv_heads, key_dim, value_dim, D, int(bool(wide)),
+                                           int(bool(unit_norm)), _f(eps), n_heads, n_kv_heads, key_dim, value_dim, D,
                                            _p(ctx.positions), _p(ctx.row_req), _p(table), table.shape[1], cache.page_size,
                                            _p(cache.pages), _dt(cache.pages), _p(q_out), _dt(q_out), int(cache.writes), T,
                                            _stream()), "rotate_norm_append")
@@ -746,8 +746,8 @@ def rotate_norm_append(proj, col0: int, cos, sin, rot: int, magnitude: float, un
 @_dispatch("head_mix_gate")
 def head_mix_gate(o, mix, proj, gate_col0: int, n_heads: int, n_kv_heads: int, value_dim: int, head_dim: int, out, ctx) -> None:
     """out[t, h * value_dim + e] = sigmoid(proj[t, gate_col0 + h * value_dim + e]) * sum_g mix[h, g] * o[t, wide(g, kv(h)), e]:
-    `o` holds, for every query head g and value head c, head g's weighted sum over the values of c (the attention's result
-    over operands laid out by `rotate_norm_append(wide=True)`), wide(g, c) = ((g // r) * n_kv_heads + c) * r + g % r with
+    `o` holds, for every query head g and value head c, head g's weighted sum over the values of c (the result of
+    `paged_attention(value_split=n_kv_heads)`), wide(g, c) = ((g // r) * n_kv_heads + c) * r + g % r with
     r = n_heads / n_kv_heads, kv(h) = h // r.  mix None: no mixing (o holds n_heads heads); proj None: no gate."""
     T = out.shape[0]
     _check(library().kf_head_mix_gate(_p(o), _p(mix), _dt(mix) if mix is not None else F32, _p(proj),

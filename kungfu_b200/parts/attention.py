@@ -168,9 +168,10 @@ class TalkingAttention(Mixer):
       y = o W_o^T
 
     Since o_h = sum_g mix[h, g] O[g, h/r] with O[g, c] the plain attention of query head g over value head c, the
-    framework's attention kernels do the work on "wide" operands: every query head once per value head, and the cache
-    holding (key head, value head) pairs; `ops.head_mix_gate` then sums over g and gates.  The cache therefore holds
-    n_kv_heads^2 heads of D = max(key_dim, value_dim).  With `mix` None the mixer is plain grouped-query attention with
+    framework's attention kernels do the work: they give every query head's weighted sum over every value head
+    (`ops.paged_attention(value_split=n_kv_heads)`, n_heads * n_kv_heads result heads from the same queries and pages);
+    `ops.head_mix_gate` then sums over g and gates.  The cache holds n_kv_heads heads of D = max(key_dim, value_dim),
+    rounded up to a size the kernels take.  With `mix` None the mixer is plain grouped-query attention with
     the same extras.  Scores, softmax, norms, rotation, mixing sums and the gate are 32-bit."""
 
     def __init__(self, w_in: torch.Tensor, wo: torch.Tensor, *, n_heads: int, n_kv_heads: int, key_dim: int, value_dim: int,
@@ -201,10 +202,10 @@ class TalkingAttention(Mixer):
             raise ValueError(f"{rot} rotary dims for keys of {self.key_dim}")
         if position is not None and getattr(position, "interleaved", False):
             raise ValueError("this mixer turns pairs (i, i + rot/2); an interleaved rotation is not supported")
-        ops.check_attention_sizes(self.n_heads * self.reps, self.n_kv_heads * self.reps, self.head_dim)
+        ops.check_attention_sizes(self.n_heads, self.n_kv_heads, self.head_dim)
 
     def state_need(self):
-        return PagedKV(self.n_kv_heads * self.reps, self.head_dim, self.window)
+        return PagedKV(self.n_kv_heads, self.head_dim, self.window)
 
     def forward(self, x, ctx, cache):
         T = x.shape[0]
@@ -217,11 +218,14 @@ class TalkingAttention(Mixer):
         else:
             cos = sin = None
             rot, mag = 0, 1.0
-        q = ctx.buf("attn_q", (T, nh * reps * D), ctx.act_dtype)
+        q = ctx.buf("attn_q", (T, nh * D), ctx.act_dtype)
         ops.rotate_norm_append(proj, 0, cos, sin, rot, mag, self.unit_norm, self.norm_eps, nh, nkv, self.key_dim,
-                               self.value_dim, self.mix is not None, ctx, cache, q)
+                               self.value_dim, ctx, cache, q)
         o = ctx.buf("attn_o", (T, nh * reps * D), ctx.act_dtype)
-        ops.paged_attention(q, o, ctx, cache, nh * reps, nkv * reps, D, self.scale, 0.0, self.window)
+        if self.mix is not None:
+            ops.paged_attention(q, o, ctx, cache, nh * nkv, nkv * nkv, D, self.scale, 0.0, self.window, value_split=nkv)
+        else:
+            ops.paged_attention(q, o, ctx, cache, nh, nkv, D, self.scale, 0.0, self.window)
         if self.mix is not None or self.gated or D != self.value_dim:
             packed = ctx.buf("attn_gated", (T, nh * self.value_dim), ctx.act_dtype)
             ops.head_mix_gate(o, self.mix, proj if self.gated else None, self.qkv_width, nh, nkv, self.value_dim, D, packed, ctx)

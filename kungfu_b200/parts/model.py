@@ -38,6 +38,7 @@ class DecoderModel(Part):
         self.schedule = list(schedule) if schedule is not None else default_schedule(len(self.layers))
         self.name = name
         self.vocab = head.vocab
+        self.after_layer = None         # an observer f(call index, residual) called after every layer run (eager steps only)
         writers: dict[int, int] = {}
         for call in self.schedule:
             if not (0 <= call.layer < len(self.layers)):
@@ -84,6 +85,8 @@ class DecoderModel(Part):
                     x, normed = block.forward(x, ctx, view, normed=normed, then=then)
                 else:
                     x, normed = block.forward(x, ctx, view), None
+            if self.after_layer is not None:
+                self.after_layer(i, x)
         if ctx.n_logits == 0:
             return None
         with ops.nvtx_range("head"):

@@ -97,11 +97,12 @@ class CpuOps:
             cache.pages[page, 0, :, pos % P, :] = k[t].to(cache.pages.dtype)
             cache.pages[page, 1, :, pos % P, :] = v[t].to(cache.pages.dtype)
 
-    def paged_attention(self, q, out, ctx, cache, nh, nkv, d, scale, softcap, window):
+    def paged_attention(self, q, out, ctx, cache, nh, nkv, d, scale, softcap, window, value_split=0):
         T = q.shape[0]
         table = ctx.block_tables[cache.group]
         P = cache.page_size
         group = nh // nkv
+        G = value_split
         for t in range(T):
             r = int(ctx.row_req[t])
             if r < 0:
@@ -115,13 +116,19 @@ class CpuOps:
             slots = [j % P for j in js]
             K = cache.pages[pages, 0, :, slots, :].float()        # [n, nkv, d]
             V = cache.pages[pages, 1, :, slots, :].float()
-            qt = q[t].float().view(nh, d)
+            qt = q[t].float().view(nh // G if G else nh, d)
             for h in range(nh):
-                s = (K[:, h // group] @ qt[h]) * scale
+                if G:                          # result head h: query head qh over key head kh and value head vh
+                    kh, vh = (h // group) // G, (h // group) % G
+                    qh = kh * group + h % group
+                else:
+                    kh = vh = h // group
+                    qh = h
+                s = (K[:, kh] @ qt[qh]) * scale
                 if softcap > 0:
                     s = softcap * torch.tanh(s / softcap)
                 p = torch.softmax(s, dim=0)
-                out[t, h * d:(h + 1) * d] = (p @ V[:, h // group]).to(out.dtype)
+                out[t, h * d:(h + 1) * d] = (p @ V[:, vh]).to(out.dtype)
 
     # ---- short convolution, q|k|v preparation, state-space scan (restatements of what the kernels of the same names do) ----------------
     @staticmethod
@@ -369,7 +376,7 @@ class CpuOps:
 
         out.copy_((a * n(z) + b * n(z * z) + c * n(z * z * z) + e).to(out.dtype))
 
-    def rotate_norm_append(self, proj, col0, cos, sin, rot, magnitude, unit_norm, eps, nh, nkv, dk, dv, wide, ctx, cache, q_out):
+    def rotate_norm_append(self, proj, col0, cos, sin, rot, magnitude, unit_norm, eps, nh, nkv, dk, dv, ctx, cache, q_out):
         T = q_out.shape[0]
         D = cache.pages.shape[-1]
         C = (nh + nkv) * dk + nkv * dv
@@ -385,13 +392,10 @@ class CpuOps:
                 y[..., rot // 2:rot] = a * s_ + b * c
             if unit_norm:
                 y.copy_(y * torch.rsqrt(y.pow(2).mean(-1, keepdim=True) + eps))
-        reps, per = (nkv if wide else 1), nh // nkv
-        qp = torch.zeros(T, nh * reps, D)
-        for g in range(nh):
-            for c in range(reps):
-                qp[:, ((g // per) * nkv + c) * per + g % per if wide else g, :dk] = q[:, g]
+        qp = torch.zeros(T, nh, D)
+        qp[:, :, :dk] = q
         qp[ctx.row_req[:T] < 0] = 0
-        q_out.copy_(qp.reshape(T, nh * reps * D).to(q_out.dtype))
+        q_out.copy_(qp.reshape(T, nh * D).to(q_out.dtype))
         if not cache.writes:
             return
         table = ctx.block_tables[cache.group]
@@ -404,11 +408,8 @@ class CpuOps:
             page = int(table[r, pos // P])
             assert page >= 0
             cache.pages[page, :, :, pos % P, :] = 0
-            for ck in range(nkv):
-                for cv in range(reps):
-                    st = ck * nkv + cv if wide else ck
-                    cache.pages[page, 0, st, pos % P, :dk] = k[t, ck].to(cache.pages.dtype)
-                    cache.pages[page, 1, st, pos % P, :dv] = v[t, cv if wide else ck].to(cache.pages.dtype)
+            cache.pages[page, 0, :, pos % P, :dk] = k[t].to(cache.pages.dtype)
+            cache.pages[page, 1, :, pos % P, :dv] = v[t].to(cache.pages.dtype)
 
     def head_mix_gate(self, o, mix, proj, gate_col0, nh, nkv, dv, D, out, ctx):
         T = out.shape[0]

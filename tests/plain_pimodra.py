@@ -11,6 +11,23 @@ import torch
 
 F = torch.float64
 
+# What a 16-bit serving path may round: the inputs of matrix products (normed rows, the heads after the attention, the
+# feed-forward's inner rows), queries, keys and values as the attention reads them, and the attention's weights.  `ROUND`
+# is applied at those places; the identity by default.  `rounded_to_bfloat16()` switches it for a block of code, which
+# gives a yardstick of how far 8-bit mantissas alone move a model's logits.
+ROUND = lambda t: t
+
+
+class rounded_to_bfloat16:
+    def __enter__(self):
+        global ROUND
+        self.saved, ROUND = ROUND, (lambda t: t.to(torch.bfloat16).to(F))
+
+    def __exit__(self, *exc):
+        global ROUND
+        ROUND = self.saved
+        return False
+
 
 def group_norm(x, weight, eps: float, groups: int):
     """x [T, W] cut into `groups` equal consecutive parts; each part is divided by sqrt(mean(part^2) + eps); then * weight."""
@@ -65,8 +82,9 @@ def talking_attention(h, m: dict, w: dict, p: str, eps: float, positions=None):
     q = (h @ w[p + "q"].to(F).T).reshape(T, H, d)
     k = (h @ w[p + "k"].to(F).T).reshape(T, G, d)
     v = (h @ w[p + "v"].to(F).T).reshape(T, G, dv)
-    q = unit_rms(rotate(q, pos, m.get("rot")), eps)
-    k = unit_rms(rotate(k, pos, m.get("rot")), eps)
+    q = ROUND(unit_rms(rotate(q, pos, m.get("rot")), eps))
+    k = ROUND(unit_rms(rotate(k, pos, m.get("rot")), eps))
+    v = ROUND(v)
     per = H // G
     kv_of = torch.arange(H) // per
     s = torch.einsum("ihd,jhd->hij", q, k[:, kv_of, :]) * float(m["scale"])
@@ -76,10 +94,10 @@ def talking_attention(h, m: dict, w: dict, p: str, eps: float, positions=None):
     if size:
         seen = seen & (i - j < int(size))
     s = s.masked_fill(~seen[None], float("-inf"))
-    a = torch.softmax(s, dim=-1)                                   # [H, T, T], each head's own weights
+    a = ROUND(torch.softmax(s, dim=-1))                            # [H, T, T], each head's own weights
     a = torch.einsum("hg,gij->hij", w[p + "talk"].to(F), a)        # heads' weights mixed after the softmax
     o = torch.einsum("hij,jhv->ihv", a, v[:, kv_of, :]).reshape(T, H * dv)
-    o = o * torch.sigmoid(h @ w[p + "g"].to(F).T)
+    o = ROUND(ROUND(o) * torch.sigmoid(h @ w[p + "g"].to(F).T))
     return o @ w[p + "o"].to(F).T
 
 
@@ -90,7 +108,7 @@ def poly_norm(z, coef, eps: float):
 
 
 def dense_ffn(h, w: dict, p: str, eps: float):
-    return poly_norm(h @ w[p + "up"].to(F).T, w[p + "act"], eps) @ w[p + "down"].to(F).T
+    return ROUND(poly_norm(h @ w[p + "up"].to(F).T, w[p + "act"], eps)) @ w[p + "down"].to(F).T
 
 
 def route(z, experts: int, top: int, groups: int, keep: int):
@@ -122,19 +140,19 @@ def moe_ffn(h, f: dict, w: dict, p: str, router_input=None):
         for c in range(top):
             e = int(ids[t, c])
             gate, up = w[f"{p}e{e}.gate"].to(F) @ h[t], w[f"{p}e{e}.up"].to(F) @ h[t]
-            y[t] += wts[t, c] * (w[f"{p}e{e}.down"].to(F) @ (gate * torch.sigmoid(gate) * up))
+            y[t] += wts[t, c] * (w[f"{p}e{e}.down"].to(F) @ ROUND(gate * torch.sigmoid(gate) * up))
     return y
 
 
 def layer(x, cfg: dict, w: dict, i: int):
     l, p = cfg["layers"][i], f"l{i}."
     eps, groups = float(cfg["norm"]["eps"]), int(cfg["norm"].get("groups", 1))
-    a = talking_attention(group_norm(x, w[p + "norm1"], eps, groups), l["mixer"], w, p + "mix.", eps)
+    a = talking_attention(ROUND(group_norm(x, w[p + "norm1"], eps, groups)), l["mixer"], w, p + "mix.", eps)
     x = x + group_norm(a, w[p + "norm1b"], eps, groups)
     f = l.get("mlp")
     if f is None:
         return x
-    h = group_norm(x, w[p + "norm2"], eps, groups)
+    h = ROUND(group_norm(x, w[p + "norm2"], eps, groups))
     y = dense_ffn(h, w, p + "mlp.", eps) if f.get("kind", "dense") == "dense" else moe_ffn(h, f, w, p + "mlp.")
     return x + group_norm(y, w[p + "norm2b"], eps, groups)
 
@@ -164,5 +182,5 @@ def forward(cfg: dict, w: dict, tokens, keep_layers: bool = False):
         x = layer(x, cfg, w, i)
         after.append(x)
     eps, groups = float(cfg["norm"]["eps"]), int(cfg["norm"].get("groups", 1))
-    logits = group_norm(x, w["final.norm"], eps, groups) @ w["embed"].to(F).T
+    logits = ROUND(group_norm(x, w["final.norm"], eps, groups)) @ w["embed"].to(F).T
     return (logits, torch.stack(after)) if keep_layers else logits
