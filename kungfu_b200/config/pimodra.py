@@ -230,7 +230,7 @@ class PimodraConfig:
         out = []
         for i, t in self.layer_runs():
             m = self.layers[i].mixer
-            stored = m.kv_heads * m.kv_heads                    # (key head, value head) pairs
+            stored = m.kv_heads
             out.append({"layer": i, "pass": t, "kind": "kv_pages", "window": m.window, "fixed_bytes": 0,
                         "bytes_per_token": 2 * stored * attention_head_size(max(m.dim, m.vdim)) * element_size})
         return out

@@ -124,14 +124,39 @@ KF_API int kf_rotate_norm_append(const float* in, int ld, int col0, const float*
 constexpr int HG_THREADS = 128;
 constexpr int HG_HEADS = 8;                                 // result heads a thread sums at a time
 
-__device__ __forceinline__ float2 hg_load2(const float* p) { return *reinterpret_cast<const float2*>(p); }
-__device__ __forceinline__ float2 hg_load2(const __nv_bfloat16* p) {
-  return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p));
+template <int VEC> struct HgVec { float v[VEC]; };
+template <int VEC> __device__ __forceinline__ HgVec<VEC> hg_load(const float* p) {
+  HgVec<VEC> r;
+  if constexpr (VEC == 4) { const float4 x = *reinterpret_cast<const float4*>(p); r.v[0] = x.x, r.v[1] = x.y, r.v[2] = x.z, r.v[3] = x.w; }
+  else { const float2 x = *reinterpret_cast<const float2*>(p); r.v[0] = x.x, r.v[1] = x.y; }
+  return r;
+}
+template <int VEC> __device__ __forceinline__ HgVec<VEC> hg_load(const __nv_bfloat16* p) {
+  HgVec<VEC> r;
+  if constexpr (VEC == 4) {
+    const uint2 x = *reinterpret_cast<const uint2*>(p);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&x.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&x.y));
+    r.v[0] = a.x, r.v[1] = a.y, r.v[2] = b.x, r.v[3] = b.y;
+  } else {
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p));
+    r.v[0] = a.x, r.v[1] = a.y;
+  }
+  return r;
+}
+__device__ __forceinline__ void hg_store4(float* p, const float* v) { *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]); }
+__device__ __forceinline__ void hg_store4(__nv_bfloat16* p, const float* v) {
+  const __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
+  uint2 x;
+  x.x = *reinterpret_cast<const uint32_t*>(&a), x.y = *reinterpret_cast<const uint32_t*>(&b);
+  *reinterpret_cast<uint2*>(p) = x;
 }
 
-// One thread per (row, value head c, pair of elements): it reads the pair of every query head's result over value head c
-// once and sums it into the r heads of c's group.  M sits in shared memory when it fits (else it is read through L1).
-template <typename TQ, typename TW>
+// One thread per (row, value head c, VEC neighbouring elements): it reads those elements of every query head's result over
+// value head c once and sums them into the r heads of c's group.  M sits in shared memory when it fits (else it is read
+// through L1).  VEC = 4 needs rows whose starts and head sizes are multiples of four elements (16-byte gate loads and
+// 8- or 16-byte stores); VEC = 2 takes every even D and any dv, with element-wise gate loads and stores.
+template <typename TQ, typename TW, int VEC>
 __global__ void __launch_bounds__(HG_THREADS)
 head_mix_gate_kernel(const TQ* __restrict__ o, const TW* __restrict__ mix, const float* __restrict__ g, int ld, int gcol0,
                      int nh, int nkv, int dv, int D, TQ* __restrict__ out, const int* __restrict__ row_req, int T,
@@ -144,55 +169,70 @@ head_mix_gate_kernel(const TQ* __restrict__ o, const TW* __restrict__ mix, const
     __syncthreads();
   }
   const int per = nh / nkv;
-  const int pairs = (dv + 1) >> 1;
+  const int chunks = (dv + VEC - 1) / VEC;
   const int groups = mix ? nkv : nh;                        // without M every head is a group of its own
   const long item = (long)blockIdx.x * HG_THREADS + threadIdx.x;
-  if (item >= (long)T * groups * pairs) return;
-  const int ip = (int)(item % pairs);
-  const int cv = (int)((item / pairs) % groups);
-  const int t = (int)(item / ((long)pairs * groups));
-  const int i = 2 * ip;
-  const bool two = i + 1 < dv;
+  if (item >= (long)T * groups * chunks) return;
+  const int ic = (int)(item % chunks);
+  const int cv = (int)((item / chunks) % groups);
+  const int t = (int)(item / ((long)chunks * groups));
+  const int i = VEC * ic;
   const bool pad = row_req[t] < 0;
-  auto put = [&](int h, float a, float b) {
+  auto put = [&](int h, float* a) {
     const size_t e = (size_t)h * dv + i;
-    if (pad) a = b = 0.f;
-    else if (g) {
-      const float* gr = g + (size_t)t * ld + gcol0 + e;
-      a *= 1.f / (1.f + expf(-gr[0]));
-      if (two) b *= 1.f / (1.f + expf(-gr[1]));
+    if constexpr (VEC == 4) {
+      if (pad) a[0] = a[1] = a[2] = a[3] = 0.f;
+      else if (g) {
+        const HgVec<4> gr = hg_load<4>(g + (size_t)t * ld + gcol0 + e);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) a[k] *= 1.f / (1.f + expf(-gr.v[k]));
+      }
+      hg_store4(out + (size_t)t * nh * dv + e, a);
+    } else {
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) {
+        if (i + k < dv) {
+          float x = pad ? 0.f : a[k];
+          if (!pad && g) x *= 1.f / (1.f + expf(-g[(size_t)t * ld + gcol0 + e + k]));
+          kf_store(out, (size_t)t * nh * dv + e + k, x);
+        }
+      }
     }
-    kf_store(out, (size_t)t * nh * dv + e, a);
-    if (two) kf_store(out, (size_t)t * nh * dv + e + 1, b);
   };
   if (!mix) {
-    const float2 v = pad ? make_float2(0.f, 0.f) : hg_load2(o + ((size_t)t * nh + cv) * D + i);
-    put(cv, v.x, v.y);
+    HgVec<VEC> v = hg_load<VEC>(o + ((size_t)t * nh + cv) * D + i);
+    put(cv, v.v);
     return;
   }
   const TQ* orow = o + (size_t)t * nh * nkv * D + i;
   for (int h0 = 0; h0 < per; h0 += HG_HEADS) {
-    float ax[HG_HEADS], ay[HG_HEADS];
+    float acc[HG_HEADS][VEC];
 #pragma unroll
-    for (int j = 0; j < HG_HEADS; ++j) ax[j] = ay[j] = 0.f;
+    for (int j = 0; j < HG_HEADS; ++j)
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) acc[j][k] = 0.f;
     if (!pad) {
-      for (int gq = 0; gq < nh; ++gq) {
-        const int wq = ((gq / per) * nkv + cv) * per + gq % per;
-        const float2 v = hg_load2(orow + (size_t)wq * D);
+      for (int kh = 0; kh < nkv; ++kh) {                    // query heads in ascending order: key head kh, then its r heads
+        const TQ* base = orow + (size_t)((kh * nkv + cv) * per) * D;
+#pragma unroll 4
+        for (int q = 0; q < per; ++q) {
+          const int gq = kh * per + q;
+          const HgVec<VEC> v = hg_load<VEC>(base + (size_t)q * D);
 #pragma unroll
-        for (int j = 0; j < HG_HEADS; ++j) {
-          if (h0 + j < per) {
-            const int mi = (cv * per + h0 + j) * nh + gq;
-            const float m = mix_in_smem ? ms[mi] : kf_load(mix, mi);
-            ax[j] = fmaf(m, v.x, ax[j]);
-            ay[j] = fmaf(m, v.y, ay[j]);
+          for (int j = 0; j < HG_HEADS; ++j) {
+            if (h0 + j < per) {
+              const int mi = (cv * per + h0 + j) * nh + gq;
+              const float m = mix_in_smem ? ms[mi] : kf_load(mix, mi);
+#pragma unroll
+              for (int k = 0; k < VEC; ++k) acc[j][k] = fmaf(m, v.v[k], acc[j][k]);
+            }
           }
         }
       }
     }
 #pragma unroll
     for (int j = 0; j < HG_HEADS; ++j)
-      if (h0 + j < per) put(cv * per + h0 + j, ax[j], ay[j]);
+      if (h0 + j < per) put(cv * per + h0 + j, acc[j]);
   }
 }
 
@@ -203,17 +243,22 @@ KF_API int kf_head_mix_gate(const void* o, const void* mix, int w_dtype, const f
   const size_t want = mix ? (size_t)nh * nh * sizeof(float) : 0;
   const int in_smem = want <= 40 * 1024;
   const size_t smem = in_smem ? want : 0;
-  const long n_work = (long)T * (mix ? nkv : nh) * ((dv + 1) / 2);
+  const bool by4 = dv % 4 == 0 && D % 4 == 0 && (!g || (ld % 4 == 0 && gcol0 % 4 == 0 && ((uintptr_t)g & 15) == 0)) &&
+                   ((uintptr_t)o & 15) == 0 && ((uintptr_t)out & 15) == 0;
+  const int vec = by4 ? 4 : 2;
+  const long n_work = (long)T * (mix ? nkv : nh) * ((dv + vec - 1) / vec);
   const dim3 grid((unsigned)((n_work + HG_THREADS - 1) / HG_THREADS));
-#define KF_GO(TQ, TW)                                                                                                \
-  kf_launch(head_mix_gate_kernel<TQ, TW>, grid, dim3(HG_THREADS), smem, stream, (const TQ*)o, (const TW*)mix, g, ld, gcol0, \
-            nh, nkv, dv, D, (TQ*)out, row_req, T, in_smem)
+#define KF_GO2(TQ, TW, VEC)                                                                                          \
+  kf_launch(head_mix_gate_kernel<TQ, TW, VEC>, grid, dim3(HG_THREADS), smem, stream, (const TQ*)o, (const TW*)mix, g, ld,  \
+            gcol0, nh, nkv, dv, D, (TQ*)out, row_req, T, in_smem)
+#define KF_GO(TQ, TW) do { if (by4) KF_GO2(TQ, TW, 4); else KF_GO2(TQ, TW, 2); } while (0)
   if (dtype == KF_F32 && w_dtype == KF_F32) KF_GO(float, float);
   else if (dtype == KF_BF16 && w_dtype == KF_BF16) KF_GO(__nv_bfloat16, __nv_bfloat16);
   else if (dtype == KF_BF16 && w_dtype == KF_F32) KF_GO(__nv_bfloat16, float);
   else if (dtype == KF_F32 && w_dtype == KF_BF16) KF_GO(float, __nv_bfloat16);
   else return KF_ERR_DTYPE;
 #undef KF_GO
+#undef KF_GO2
   KF_CHECK_LAUNCH();
   return KF_OK;
 }

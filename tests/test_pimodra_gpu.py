@@ -136,6 +136,84 @@ def test_silu_gated_experts_as_grouped_products(dtype, T, E, top, W, ff):
     assert _rel(y, ref) < (2e-5 if dtype == "float32" else 1e-2)
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("H,G,d,P,window", [(4, 2, 16, 4, 9), (3, 3, 32, 16, None), (8, 2, 64, 64, 100), (4, 1, 64, 64, None),
+                                            (8, 4, 128, 64, 70), (6, 3, 48, 8, 24), (40, 2, 64, 64, None)])
+def test_every_query_head_over_every_value_head(dtype, H, G, d, P, window):
+    """`paged_attention(value_split=G)`: H * G result heads from H query heads and G stored heads, on every kernel the step
+    would choose (whole prompts, rows in the middle of a prompt, single decode rows; 40 heads over 2: the decode kernel
+    without tensor cores).  The reference attends head by head with the keys of the query's head and the values of each."""
+    import math
+    import test_gpu_kernels as tk
+    from kungfu_b200 import ops
+    tdt = DTYPES[dtype]
+    lens = [1, 37, 150, 70, 200]
+    pages, table, ks, vs = tk._paged_setup(tdt, H, G, d, P, lens, seed=15)         # pages of G heads
+    per = H // G
+    scale = 1.0 / math.sqrt(d)
+    g = torch.Generator().manual_seed(16)
+
+    def run(rows, dec_rows, pre_rows):
+        q = torch.randn(len(rows), H, d, generator=g).to(tdt)
+        ctx = tk._Ctx(torch.tensor([p for _, p in rows], dtype=torch.int32, device=DEV),
+                      torch.tensor([r for r, _ in rows], dtype=torch.int32, device=DEV), table.to(DEV), dec_rows, pre_rows)
+        out = torch.empty(len(rows), H * G * d, dtype=tdt, device=DEV)
+        ops.paged_attention(q.view(len(rows), H * d).to(DEV), out, ctx, tk._View(pages.to(DEV), P), H * G, G * G, d, scale, 0.0,
+                            window, value_split=G)
+        got = out.view(len(rows), H * G, d).double().cpu()
+        for i, (r, pos) in enumerate(rows):
+            lo = max(0, pos - window + 1) if window else 0
+            for gq in range(H):
+                kh = gq // per
+                a = torch.softmax((ks[r][lo:pos + 1, kh].double() @ q[i, gq].double()) * scale, 0)
+                for c in range(G):
+                    want = a @ vs[r][lo:pos + 1, c].double()
+                    wide = (kh * G + c) * per + gq % per
+                    err = float((got[i, wide] - want).abs().max()) / max(float(want.abs().max()), 1e-6)
+                    assert err < (2e-5 if dtype == "float32" else 2e-2), (i, gq, c, err)
+
+    # a whole prompt, the tail of another, and single rows of three requests in one step
+    rows = [(1, p) for p in range(37)] + [(3, p) for p in range(50, 70)] + [(2, 149), (0, 0), (4, 199)]
+    run(rows, [57, 58, 59], list(range(57)))
+    run([(2, 149), (0, 0), (4, 199), (3, 69)], [0, 1, 2, 3], None)                 # a decode step
+    run([(4, p) for p in range(200)], None, list(range(200)))                      # a long prompt alone
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("H,G,dv,D,gate,mixed", [(4, 2, 24, 32, True, True), (3, 3, 12, 16, True, True), (4, 1, 64, 64, True, True),
+                                                 (8, 4, 64, 128, True, True), (2, 2, 7, 16, True, True), (36, 2, 6, 16, False, True),
+                                                 (112, 8, 8, 16, True, True), (5, 5, 16, 16, True, False), (3, 1, 5, 32, False, False)])
+def test_heads_mixed_and_gated(dtype, H, G, dv, D, gate, mixed):
+    """`head_mix_gate` alone: rows of 2 and 4 elements per thread, odd value sizes, 18 heads per value head (more than a
+    thread sums at once), a mixing matrix too large for shared memory, no gate, no mixing, and a padding row."""
+    from kungfu_b200 import ops
+    import test_petanex_gpu as other
+    st = other.FakeStep(rows=(6, 1, 4))
+    T = st.n_rows
+    tdt = DTYPES[dtype]
+    g = torch.Generator().manual_seed(H * 100 + dv)
+    per = H // G
+    o = torch.randn(T, H * (G if mixed else 1), D, generator=g).to(tdt)
+    mix = (torch.eye(H) + 0.4 * torch.randn(H, H, generator=g)).to(tdt) if mixed else None
+    gcol0 = 8
+    proj = torch.randn(T, gcol0 + H * dv + 4, generator=g)
+    out = torch.full((T, H * dv), 7.0, dtype=tdt, device=DEV)
+    ops.head_mix_gate(o.reshape(T, -1).to(DEV), None if mix is None else mix.to(DEV), proj.to(DEV) if gate else None, gcol0, H, G,
+                      dv, D, out, st)
+    want = torch.zeros(T, H, dv, dtype=torch.float64)
+    for h in range(H):
+        if mixed:
+            for gq in range(H):
+                want[:, h] += float(mix[h, gq]) * o[:, ((gq // per) * G + h // per) * per + gq % per, :dv].double()
+        else:
+            want[:, h] = o[:, h, :dv].double()
+    want = want.reshape(T, H * dv)
+    if gate:
+        want = want * torch.sigmoid(proj[:, gcol0:gcol0 + H * dv].double())
+    want[-1] = 0                                              # the padding row
+    assert _rel(out, want) < (3e-6 if dtype == "float32" else 1e-2)
+
+
 # ---- the model through the step function -------------------------------------------------------------------------
 
 def _runner(folder, dtype, page, max_tokens, max_requests=4, graphs=True, ctx=2048):
