@@ -122,7 +122,8 @@ KF_API int kf_rotate_norm_append(const float* in, int ld, int col0, const float*
 }
 
 constexpr int HG_THREADS = 128;
-constexpr int HG_HEADS = 8;                                 // result heads a thread sums at a time
+constexpr int HG_LOADS = 8;                                 // loads a thread has in flight
+constexpr int HG_HEADS = 4;                                 // result heads a thread sums at a time
 
 template <int VEC> struct HgVec { float v[VEC]; };
 template <int VEC> __device__ __forceinline__ HgVec<VEC> hg_load(const float* p) {
@@ -144,6 +145,20 @@ template <int VEC> __device__ __forceinline__ HgVec<VEC> hg_load(const __nv_bflo
   }
   return r;
 }
+// The same elements as they lie in memory (converted when they are used, so that eight loads in flight cost few registers).
+template <typename T, int VEC> struct HgRaw;
+template <> struct HgRaw<float, 4> { float4 r; __device__ void load(const float* p) { r = *reinterpret_cast<const float4*>(p); }
+  __device__ void get(float* v) const { v[0] = r.x, v[1] = r.y, v[2] = r.z, v[3] = r.w; } };
+template <> struct HgRaw<float, 2> { float2 r; __device__ void load(const float* p) { r = *reinterpret_cast<const float2*>(p); }
+  __device__ void get(float* v) const { v[0] = r.x, v[1] = r.y; } };
+template <> struct HgRaw<__nv_bfloat16, 4> { uint2 r; __device__ void load(const __nv_bfloat16* p) { r = *reinterpret_cast<const uint2*>(p); }
+  __device__ void get(float* v) const {
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&r.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&r.y));
+    v[0] = a.x, v[1] = a.y, v[2] = b.x, v[3] = b.y; } };
+template <> struct HgRaw<__nv_bfloat16, 2> { uint32_t r; __device__ void load(const __nv_bfloat16* p) { r = *reinterpret_cast<const uint32_t*>(p); }
+  __device__ void get(float* v) const { const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&r)); v[0] = a.x, v[1] = a.y; } };
+
 __device__ __forceinline__ void hg_store4(float* p, const float* v) { *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]); }
 __device__ __forceinline__ void hg_store4(__nv_bfloat16* p, const float* v) {
   const __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
@@ -157,7 +172,7 @@ __device__ __forceinline__ void hg_store4(__nv_bfloat16* p, const float* v) {
 // through L1).  VEC = 4 needs rows whose starts and head sizes are multiples of four elements (16-byte gate loads and
 // 8- or 16-byte stores); VEC = 2 takes every even D and any dv, with element-wise gate loads and stores.
 template <typename TQ, typename TW, int VEC>
-__global__ void __launch_bounds__(HG_THREADS)
+__global__ void __launch_bounds__(HG_THREADS, 5)
 head_mix_gate_kernel(const TQ* __restrict__ o, const TW* __restrict__ mix, const float* __restrict__ g, int ld, int gcol0,
                      int nh, int nkv, int dv, int D, TQ* __restrict__ out, const int* __restrict__ row_req, int T,
                      int mix_in_smem) {
@@ -212,19 +227,29 @@ head_mix_gate_kernel(const TQ* __restrict__ o, const TW* __restrict__ mix, const
 #pragma unroll
       for (int k = 0; k < VEC; ++k) acc[j][k] = 0.f;
     if (!pad) {
-      for (int kh = 0; kh < nkv; ++kh) {                    // query heads in ascending order: key head kh, then its r heads
-        const TQ* base = orow + (size_t)((kh * nkv + cv) * per) * D;
-#pragma unroll 4
-        for (int q = 0; q < per; ++q) {
-          const int gq = kh * per + q;
-          const HgVec<VEC> v = hg_load<VEC>(base + (size_t)q * D);
+      const int hn = min(HG_HEADS, per - h0);               // heads of this pass
+      const int m0 = (cv * per + h0) * nh;                  // M[first head of the pass, 0]
+      int kh = 0, q = 0;                                    // query head gq = kh * r + q, in ascending order
+      for (int g0 = 0; g0 < nh; g0 += HG_LOADS) {
+        HgRaw<TQ, VEC> raw[HG_LOADS];
 #pragma unroll
-          for (int j = 0; j < HG_HEADS; ++j) {
-            if (h0 + j < per) {
-              const int mi = (cv * per + h0 + j) * nh + gq;
+        for (int u = 0; u < HG_LOADS; ++u) {                // the loads of eight query heads first, then their sums
+          if (g0 + u < nh) {
+            raw[u].load(orow + (size_t)((kh * nkv + cv) * per + q) * D);
+            if (++q == per) q = 0, ++kh;
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < HG_LOADS; ++u) {
+          if (g0 + u < nh) {
+            float v[VEC];
+            raw[u].get(v);
+#pragma unroll
+            for (int j = 0; j < HG_HEADS; ++j) {
+              const int mi = m0 + (j < hn ? j : 0) * nh + g0 + u;   // heads past the pass repeat its first: summed, never stored
               const float m = mix_in_smem ? ms[mi] : kf_load(mix, mi);
 #pragma unroll
-              for (int k = 0; k < VEC; ++k) acc[j][k] = fmaf(m, v.v[k], acc[j][k]);
+              for (int k = 0; k < VEC; ++k) acc[j][k] = fmaf(m, v[k], acc[j][k]);
             }
           }
         }
