@@ -478,7 +478,24 @@ def paged_attention(q, out, ctx, cache, n_heads: int, n_kv_heads: int, head_dim:
               _f(scale), _f(softcap), int(window or 0), int(value_split))
     n_dec = getattr(ctx, "n_dec_rows", 0)
     fast = (use_fast_attention and q.dtype == torch.bfloat16 and pages.dtype == torch.bfloat16)
-    if fast and n_dec > 0 and lib.kf_attention_decode_supported(head_dim):
+    vs_splits = ctypes.c_int(0)
+    own = decode_value_split_kernel if decode_value_split_kernel is not None else value_split >= 3
+    if (fast and n_dec > 0 and value_split and softcap == 0.0 and own
+            and lib.kf_attention_decode_vs_plan(n_dec, n_heads // value_split, value_split, head_dim,
+                                                int(min(ctx.max_kv_len, window) if window else ctx.max_kv_len),
+                                                ctypes.byref(vs_splits)) == 0):
+        # one block per tile of 16 query heads and all value heads: scores once, keys and values read once per tile
+        partial = _partial(q.device, T * n_heads * vs_splits.value * (head_dim + 4)) if vs_splits.value > 1 else None
+        items = None if n_dec == T else ctx.dec_rows
+        _check(lib.kf_attention_decode_vs(_p(q), _p(out), _p(pages), _p(items), n_dec, *common[:5], n_heads // value_split,
+                                          value_split, head_dim, _f(scale), int(window or 0), vs_splits.value, _p(partial),
+                                          _stream()), "attention (decode, every value head)")
+        if vs_splits.value > 1:
+            add_launches(1)
+        if n_dec == T:
+            return
+        rest, n_rest = ctx.pre_rows, ctx.n_pre_rows
+    elif fast and n_dec > 0 and lib.kf_attention_decode_supported(head_dim):
         ht, splits = ctypes.c_int(0), ctypes.c_int(0)
         max_keys = min(ctx.max_kv_len, window) if window else ctx.max_kv_len
         group = n_heads // n_kv_heads
@@ -531,6 +548,10 @@ def paged_attention(q, out, ctx, cache, n_heads: int, n_kv_heads: int, head_dim:
            "attention (generic)")
 
 
+# Decode rows of value-split attention: True, the kernel that owns all value heads of a tile of query heads; False, the
+# ordinary decode kernels (one block per pair of a key head and a value head); None, the former from three value heads on
+# (at one or two the pairs are so few that the ordinary kernels, which need no merge launch, are faster).
+decode_value_split_kernel = {"1": True, "0": False}.get(os.environ.get("KUNGFU_DECODE_VALUE_SPLIT", ""), None)
 fuse_rope_into_decode = os.environ.get("KUNGFU_FUSE_ROPE", "1") != "0"   # False: rotation and append always run as their own kernel
 
 

@@ -139,15 +139,18 @@ def test_silu_gated_experts_as_grouped_products(dtype, T, E, top, W, ff):
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("H,G,d,P,window", [(4, 2, 16, 4, 9), (3, 3, 32, 16, None), (8, 2, 64, 64, 100), (4, 1, 64, 64, None),
                                             (8, 4, 128, 64, 70), (6, 3, 48, 8, 24), (40, 2, 64, 64, None)])
-def test_every_query_head_over_every_value_head(dtype, H, G, d, P, window):
+@pytest.mark.parametrize("own_decode_kernel", [True, False])
+def test_every_query_head_over_every_value_head(dtype, H, G, d, P, window, own_decode_kernel, monkeypatch):
     """`paged_attention(value_split=G)`: H * G result heads from H query heads and G stored heads, on every kernel the step
-    would choose (whole prompts, rows in the middle of a prompt, single decode rows; 40 heads over 2: the decode kernel
-    without tensor cores).  The reference attends head by head with the keys of the query's head and the values of each."""
+    would choose (whole prompts, rows in the middle of a prompt, single decode rows with the keys in one part and cut
+    into several; 40 heads over 2: tiles of heads that straddle two key heads, or the decode kernel without tensor cores).  The reference attends head by head with the keys of the query's head and the values of each."""
     import math
     import test_gpu_kernels as tk
     from kungfu_b200 import ops
+    # decode rows: the kernel that owns all value heads of a tile of query heads, or the ordinary decode kernels
+    monkeypatch.setattr(ops, "decode_value_split_kernel", own_decode_kernel)
     tdt = DTYPES[dtype]
-    lens = [1, 37, 150, 70, 200]
+    lens = [1, 37, 150, 70, 200, 1500]
     pages, table, ks, vs = tk._paged_setup(tdt, H, G, d, P, lens, seed=15)         # pages of G heads
     per = H // G
     scale = 1.0 / math.sqrt(d)
@@ -176,6 +179,7 @@ def test_every_query_head_over_every_value_head(dtype, H, G, d, P, window):
     rows = [(1, p) for p in range(37)] + [(3, p) for p in range(50, 70)] + [(2, 149), (0, 0), (4, 199)]
     run(rows, [57, 58, 59], list(range(57)))
     run([(2, 149), (0, 0), (4, 199), (3, 69)], [0, 1, 2, 3], None)                 # a decode step
+    run([(5, 1499), (0, 0), (5, 1200), (1, 36)], [0, 1, 2, 3], None)               # long rows: the keys cut into many parts
     run([(4, p) for p in range(200)], None, list(range(200)))                      # a long prompt alone
 
 
