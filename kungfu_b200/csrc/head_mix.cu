@@ -22,7 +22,18 @@
 constexpr int HM_MAX_D = 256;
 constexpr int HM_WARPS = 4;
 
-template <typename TQ, typename TKV>
+__device__ __forceinline__ void hm_store4(float* p, const float* v) { *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]); }
+__device__ __forceinline__ void hm_store4(__nv_bfloat16* p, const float* v) {
+  const __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
+  uint2 x;
+  x.x = *reinterpret_cast<const uint32_t*>(&a), x.y = *reinterpret_cast<const uint32_t*>(&b);
+  *reinterpret_cast<uint2*>(p) = x;
+}
+
+// One warp per (row, head of q, k or v).  W = 4: a lane holds 4 neighbouring elements per 128 (16-byte loads, 8- or 16-byte
+// stores; head sizes and row starts must be multiples of four elements); W = 1: element lane + 32 k, any sizes.  The head is
+// staged in shared memory either way, so that a lane can read its elements' rotation partners.
+template <typename TQ, typename TKV, int W>
 __global__ void __launch_bounds__(HM_WARPS * 32)
 rotate_norm_append_kernel(const float* __restrict__ in, int ld, int col0, const float* __restrict__ cos_t,
                           const float* __restrict__ sin_t, int rot, float mag, int unit_norm, float eps, int nh, int nkv,
@@ -31,7 +42,8 @@ rotate_norm_append_kernel(const float* __restrict__ in, int ld, int col0, const 
                           int page_size, TKV* __restrict__ pages, TQ* __restrict__ q_out, int write_kv, int T) {
   kf_pdl_trigger();
   kf_pdl_wait();
-  __shared__ float hs[HM_WARPS][HM_MAX_D];
+  constexpr int NK = HM_MAX_D / (32 * W);                   // groups of W elements per lane
+  __shared__ __align__(16) float hs[HM_WARPS][HM_MAX_D];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int slots = nh + 2 * nkv;
   const long item = (long)blockIdx.x * HM_WARPS + warp;
@@ -40,6 +52,7 @@ rotate_norm_append_kernel(const float* __restrict__ in, int ld, int col0, const 
   const int req = row_req[t];
   const int kind = hslot < nh ? 0 : (hslot < nh + nkv ? 1 : 2);            // query, key, value
   const int head = kind == 0 ? hslot : (kind == 1 ? hslot - nh : hslot - nh - nkv);
+  float v[NK][W];
   if (req < 0) {                                            // padding row: zero queries, nothing filed
     if (kind == 0)
       for (int i = lane; i < D; i += 32) kf_store(q_out, ((size_t)t * nh + head) * D + i, 0.f);
@@ -49,31 +62,41 @@ rotate_norm_append_kernel(const float* __restrict__ in, int ld, int col0, const 
   const int d = kind == 2 ? dv : dk;
   const float* src = in + (size_t)t * ld + col0 + (kind == 0 ? head * dk : (kind == 1 ? (nh + head) * dk : (nh + nkv) * dk + head * dv));
   float* x = hs[warp];
-  for (int i = lane; i < d; i += 32) x[i] = src[i];
+#pragma unroll
+  for (int k = 0; k < NK; ++k) {
+    const int i0 = (lane + 32 * k) * W;
+    if (i0 < d) {
+      if constexpr (W == 4) *reinterpret_cast<float4*>(x + i0) = *reinterpret_cast<const float4*>(src + i0);
+      else x[i0] = src[i0];
+    }
+  }
   __syncwarp();
   const int half = rot >> 1;
+  const float* c = cos_t + (size_t)t * half;
+  const float* s = sin_t + (size_t)t * half;
   float ss = 0.f;
-  float v[HM_MAX_D / 32];
 #pragma unroll
-  for (int k = 0; k < HM_MAX_D / 32; ++k) {
-    const int i = lane + 32 * k;
-    float y = 0.f;
-    if (i < d) {
-      y = x[i];
-      if (kind != 2 && i < rot) {
-        const float* c = cos_t + (size_t)t * half;
-        const float* s = sin_t + (size_t)t * half;
-        y = i < half ? x[i] * (c[i] * mag) - x[i + half] * (s[i] * mag) : x[i] * (c[i - half] * mag) + x[i - half] * (s[i - half] * mag);
+  for (int k = 0; k < NK; ++k) {
+#pragma unroll
+    for (int e = 0; e < W; ++e) {
+      const int i = (lane + 32 * k) * W + e;
+      float y = 0.f;
+      if (i < d) {
+        y = x[i];
+        if (kind != 2 && i < rot)
+          y = i < half ? x[i] * (c[i] * mag) - x[i + half] * (s[i] * mag) : x[i] * (c[i - half] * mag) + x[i - half] * (s[i - half] * mag);
+        ss = fmaf(y, y, ss);
       }
-      ss = fmaf(y, y, ss);
+      v[k][e] = y;
     }
-    v[k] = y;
   }
   if (kind != 2 && unit_norm) {
     ss = kf_warp_sum(ss);
     const float inv = 1.f / sqrtf(ss / (float)d + eps);
 #pragma unroll
-    for (int k = 0; k < HM_MAX_D / 32; ++k) v[k] *= inv;
+    for (int k = 0; k < NK; ++k)
+#pragma unroll
+      for (int e = 0; e < W; ++e) v[k][e] *= inv;
   }
   int page = -1, in_page = 0;
   if (kind != 0) {
@@ -82,21 +105,18 @@ rotate_norm_append_kernel(const float* __restrict__ in, int ld, int col0, const 
     in_page = pos % page_size;
     if (page < 0) return;                                   // never for a reserved position; guards the store
   }
-  if (kind == 0) {
-    TQ* o = q_out + ((size_t)t * nh + head) * D;
+  auto put = [&](auto* o) {
 #pragma unroll
-    for (int k = 0; k < HM_MAX_D / 32; ++k) {
-      const int i = lane + 32 * k;
-      if (i < D) kf_store(o, i, v[k]);
+    for (int k = 0; k < NK; ++k) {
+      const int i0 = (lane + 32 * k) * W;
+      if (i0 < D) {
+        if constexpr (W == 4) hm_store4(o + i0, v[k]);
+        else kf_store(o, i0, v[k][0]);
+      }
     }
-  } else {
-    TKV* o = pages + ((((size_t)page * 2 + (kind - 1)) * nkv + head) * page_size + in_page) * D;
-#pragma unroll
-    for (int k = 0; k < HM_MAX_D / 32; ++k) {
-      const int i = lane + 32 * k;
-      if (i < D) kf_store(o, i, v[k]);
-    }
-  }
+  };
+  if (kind == 0) put(q_out + ((size_t)t * nh + head) * D);
+  else put(pages + ((((size_t)page * 2 + (kind - 1)) * nkv + head) * page_size + in_page) * D);
 }
 
 KF_API int kf_rotate_norm_append(const float* in, int ld, int col0, const float* cos_t, const float* sin_t, int rot, float mag,
@@ -109,14 +129,18 @@ KF_API int kf_rotate_norm_append(const float* in, int ld, int col0, const float*
   if (rot > 0 && (!cos_t || !sin_t)) return KF_ERR_SIZE;
   const long n_work = (long)T * (nh + 2 * nkv);
   const dim3 grid((unsigned)((n_work + HM_WARPS - 1) / HM_WARPS));
-#define KF_GO(TQ, TKV)                                                                                                   \
-  kf_launch(rotate_norm_append_kernel<TQ, TKV>, grid, dim3(HM_WARPS * 32), 0, stream, in, ld, col0, cos_t, sin_t, rot, mag, \
+  const bool by4 = dk % 4 == 0 && dv % 4 == 0 && D % 4 == 0 && ld % 4 == 0 && col0 % 4 == 0 && ((uintptr_t)in & 15) == 0 &&
+                   ((uintptr_t)pages & 15) == 0 && ((uintptr_t)q_out & 15) == 0;
+#define KF_GO1(TQ, TKV, W)                                                                                                \
+  kf_launch(rotate_norm_append_kernel<TQ, TKV, W>, grid, dim3(HM_WARPS * 32), 0, stream, in, ld, col0, cos_t, sin_t, rot, mag, \
             unit_norm, eps, nh, nkv, dk, dv, D, positions, row_req, block_table, table_stride, page_size,           \
             (TKV*)pages, (TQ*)q_out, write_kv, T)
+#define KF_GO(TQ, TKV) do { if (by4) KF_GO1(TQ, TKV, 4); else KF_GO1(TQ, TKV, 1); } while (0)
   if (q_dtype == KF_F32 && kv_dtype == KF_F32) KF_GO(float, float);
   else if (q_dtype == KF_BF16 && kv_dtype == KF_BF16) KF_GO(__nv_bfloat16, __nv_bfloat16);
   else return KF_ERR_DTYPE;
 #undef KF_GO
+#undef KF_GO1
   KF_CHECK_LAUNCH();
   return KF_OK;
 }
