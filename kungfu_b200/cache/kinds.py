@@ -8,6 +8,8 @@ wherever its mixer is defined (a test file is enough): the manager has no list o
 A *paged* kind stores something for every token, in pages that the manager hands out; its answers:
   window(need)                          -> tokens that stay readable (None: all); needs with equal windows share a
                                            group, i.e. a pool of page ids and one block table per request
+  keep_first(need)  (optional)          -> tokens at the start of a request that stay readable behind the window (0);
+                                           needs of one group agree on it too
   page_shape(need, page_size)           -> shape of one page of one cache slot
   page_bytes(need, page_size, elsize)   -> its bytes (elsize: bytes of the cache's element type)
   dtype(need, cache_dtype)              -> element type of the storage
@@ -46,6 +48,9 @@ class PagedKVKind:
     def window(self, need):
         return need.window
 
+    def keep_first(self, need):
+        return int(getattr(need, "keep_first", 0) or 0) if need.window is not None else 0
+
     def page_shape(self, need, page_size):
         return (2, need.n_kv_heads, page_size, need.head_dim)
 
@@ -73,6 +78,22 @@ class FixedStateKind:
 
     def view(self, storage, writes, need):
         return FixedStateView(storage, writes)
+
+
+def lifetime_of(need, kind):
+    """What names a paged need's group: its window alone, or (window, kept first tokens) when some are kept.  The
+    window and the kept tokens themselves are `lifetime_window` and `lifetime_keep` of that key."""
+    window = kind.window(need)
+    keep = int(kind.keep_first(need)) if (window is not None and hasattr(kind, "keep_first")) else 0
+    return (window, keep) if keep > 0 else window
+
+
+def lifetime_window(key):
+    return key[0] if isinstance(key, tuple) else key
+
+
+def lifetime_keep(key) -> int:
+    return key[1] if isinstance(key, tuple) else 0
 
 
 def flatten_need(need) -> list:

@@ -28,7 +28,7 @@ import numpy as np
 import torch
 
 from ..parts.base import StateBundle
-from .kinds import FixedStateView, PagedKVView, flatten_need, kind_of       # the views are re-exported from here
+from .kinds import FixedStateView, PagedKVView, flatten_need, kind_of, lifetime_keep, lifetime_of, lifetime_window       # the views are re-exported from here
 
 _OK, _E_NOT_LIVE, _E_ALREADY_LIVE, _E_NO_SLOT, _E_OUT_OF_PAGES, _E_CONTEXT, _E_COMMIT, _E_PAGE, _E_INCONSISTENT = range(9)
 
@@ -185,7 +185,7 @@ class CacheManager:
             for need in flatten_need(whole):
                 kind = kind_of(need)
                 if kind.paged:
-                    window = kind.window(need)
+                    window = lifetime_of(need, kind)         # the window, or (window, kept first tokens)
                     g = by_window.get(window)
                     if g is None:
                         if isinstance(n_pages, dict):
@@ -211,10 +211,13 @@ class CacheManager:
                 stores = [u[2] for u in self._units[s]]
                 self.storage[s] = stores if isinstance(whole, StateBundle) else stores[0]
         G = len(self.groups)
-        windows = (ctypes.c_int * max(G, 1))(*[(-1 if g.window is None else int(g.window)) for g in self.groups])
+        windows = (ctypes.c_int * max(G, 1))(*[(-1 if g.window is None else int(lifetime_window(g.window))) for g in self.groups])
         sizes = (ctypes.c_int * max(G, 1))(*pool_sizes)
         self._h = ctypes.c_void_p(self._lib.kf_cache_create(G, windows, sizes, self.page_size, self.max_requests,
                                                             self.max_context))
+        for gi, g in enumerate(self.groups):
+            if lifetime_keep(g.window) > 0:
+                self._lib.kf_cache_keep_first(self._h, gi, int(lifetime_keep(g.window)))
         self.table_width = self._lib.kf_cache_width(self._h)
         # the native block-table mirrors, [max_requests, table_width] per group, as numpy views (no copy)
         self._table_np = [np.ctypeslib.as_array(self._lib.kf_cache_mirror(self._h, g), shape=(self.max_requests, self.table_width))

@@ -72,7 +72,7 @@ def plan_cache(needs: list, *, page_size: int, parallel: int, ctx: int, batch: i
     """`needs[s]`: the state need of cache slot s (or None).  `pool_tokens`, when given, replaces `parallel * ctx` as
     the size of a group without a window (a caller that knows its requests are short).  `budget_bytes`: what the
     cache may take (None: no limit)."""
-    from .kinds import flatten_need, kind_of
+    from .kinds import flatten_need, kind_of, lifetime_keep, lifetime_of, lifetime_window
     groups: dict = {}
     order: list = []
     fixed = 0
@@ -81,14 +81,15 @@ def plan_cache(needs: list, *, page_size: int, parallel: int, ctx: int, batch: i
         if not kind.paged:
             fixed += parallel * kind.fixed_bytes(need)
             continue
-        window = kind.window(need)
+        window = lifetime_of(need, kind)             # the group's key: the window, or (window, kept first tokens)
         g = groups.get(window)
         if g is None:
             if window is None:
                 per_req = _ceil_div(ctx, page_size) * page_size
             else:
+                kept = _ceil_div(lifetime_keep(window), page_size) * page_size
                 per_req = min(_ceil_div(ctx, page_size) * page_size,
-                              _ceil_div(window + min(batch, ctx) + page_size, page_size) * page_size)
+                              _ceil_div(lifetime_window(window) + min(batch, ctx) + page_size, page_size) * page_size + kept)
             g = groups[window] = GroupPlan(window, per_req, 0, 0)
             order.append(window)
         if s not in g.slots:

@@ -6,6 +6,9 @@
 // crates/kf-backend-cuda/src/kernels/attention.cu:156, scores/softcap :80-81, lane-per-key online softmax :68-103):
 //   s_j = (q . k_j) * scale;  s_j = cap * tanh(s_j / cap) if cap > 0
 //   o   = sum_j softmax(s)_j v_j,  zeros if no key is visible.
+// keep_first > 0 (with a window): keys 0..keep_first-1 stay visible behind the window, at their true positions, so the
+// warp walks [0, min(keep_first, lo)) and then [lo, p].  sink != 0: the softmax's denominator has one more term, exp(0)
+// (a key of score 0 without a value): the walk starts from maximum 0 and sum 1.
 // The order of every sum is fixed by (row, head) alone, so a row's result does not depend on how the
 // step was cut or what else is in the batch.  This is the engine's 32-bit attention and the fallback of
 // the bfloat16 path for head sizes the tensor-core kernels do not take.
@@ -19,7 +22,8 @@ __global__ void __launch_bounds__(WARPS * 32)
 attention_generic_kernel(const TQ* __restrict__ q, TQ* __restrict__ out, const TKV* __restrict__ pages,
                          const int* __restrict__ items, const int* __restrict__ positions,
                          const int* __restrict__ row_req, const int* __restrict__ block_table, int table_stride,
-                         int page_size, int nh, int nkv, int d, float scale, float softcap, int window, int vsplit, int T) {
+                         int page_size, int nh, int nkv, int d, float scale, float softcap, int window, int vsplit,
+                         int keep_first, int sink, int T) {
   kf_pdl_trigger();
   kf_pdl_wait();
   __shared__ float qs[WARPS][MAX_D];
@@ -44,42 +48,46 @@ attention_generic_kernel(const TQ* __restrict__ q, TQ* __restrict__ out, const T
 
   const int* table = block_table + (size_t)req * table_stride;
   const size_t head_stride = (size_t)page_size * d;
-  float m = -INFINITY, l = 0.f;
+  float m = sink ? 0.f : -INFINITY, l = sink ? 1.f : 0.f;
   float acc[MAX_D / 32];
 #pragma unroll
   for (int r = 0; r < MAX_D / 32; ++r) acc[r] = 0.f;
 
-  for (int c0 = lo; c0 <= pos; c0 += 32) {
-    const int j = c0 + lane;
-    const bool valid = j <= pos;
-    long kofs = -1;                                         // element offset of key j's row
-    float s = -INFINITY;
-    if (valid) {
-      const int page = table[j / page_size];
-      kofs = (((long)page * 2) * hm.n_stored + hm.key) * (long)head_stride + (long)(j % page_size) * d;
-      const TKV* kr = pages + kofs;
-      float dot = 0.f;
-      for (int i = 0; i < d; ++i) dot = fmaf(qs[warp][i], kf_load(kr, i), dot);
-      s = kf_softcap(dot * scale, softcap);
-    }
-    const float m_new = fmaxf(m, kf_warp_max(s));
-    const float p = valid ? expf(s - m_new) : 0.f;
-    const float corr = (m == -INFINITY) ? 0.f : expf(m - m_new);
-    l = l * corr + kf_warp_sum(p);
-#pragma unroll
-    for (int r = 0; r < MAX_D / 32; ++r) acc[r] *= corr;
-    const int n = min(32, pos - c0 + 1);
-    for (int u = 0; u < n; ++u) {
-      const float pu = __shfl_sync(0xffffffffu, p, u);
-      const long vofs = __shfl_sync(0xffffffffu, kofs, u) + (long)(hm.n_stored + hm.value - hm.key) * (long)head_stride;
-      const TKV* vr = pages + vofs;
-#pragma unroll
-      for (int r = 0; r < MAX_D / 32; ++r) {
-        const int i = lane + 32 * r;
-        if (i < d) acc[r] = fmaf(pu, kf_load(vr, i), acc[r]);
+  const int kept = min(keep_first, lo);                     // keys [0, kept) are seen behind the window
+  for (int seg = kept > 0 ? 0 : 1; seg < 2; ++seg) {
+    const int first = seg == 0 ? 0 : lo, last = seg == 0 ? kept - 1 : pos;
+    for (int c0 = first; c0 <= last; c0 += 32) {
+      const int j = c0 + lane;
+      const bool valid = j <= last;
+      long kofs = -1;                                       // element offset of key j's row
+      float s = -INFINITY;
+      if (valid) {
+        const int page = table[j / page_size];
+        kofs = (((long)page * 2) * hm.n_stored + hm.key) * (long)head_stride + (long)(j % page_size) * d;
+        const TKV* kr = pages + kofs;
+        float dot = 0.f;
+        for (int i = 0; i < d; ++i) dot = fmaf(qs[warp][i], kf_load(kr, i), dot);
+        s = kf_softcap(dot * scale, softcap);
       }
+      const float m_new = fmaxf(m, kf_warp_max(s));
+      const float p = valid ? expf(s - m_new) : 0.f;
+      const float corr = (m == -INFINITY) ? 0.f : expf(m - m_new);
+      l = l * corr + kf_warp_sum(p);
+#pragma unroll
+      for (int r = 0; r < MAX_D / 32; ++r) acc[r] *= corr;
+      const int n = min(32, last - c0 + 1);
+      for (int u = 0; u < n; ++u) {
+        const float pu = __shfl_sync(0xffffffffu, p, u);
+        const long vofs = __shfl_sync(0xffffffffu, kofs, u) + (long)(hm.n_stored + hm.value - hm.key) * (long)head_stride;
+        const TKV* vr = pages + vofs;
+#pragma unroll
+        for (int r = 0; r < MAX_D / 32; ++r) {
+          const int i = lane + 32 * r;
+          if (i < d) acc[r] = fmaf(pu, kf_load(vr, i), acc[r]);
+        }
+      }
+      m = m_new;
     }
-    m = m_new;
   }
   const float inv = l > 0.f ? 1.f / l : 0.f;
 #pragma unroll
@@ -93,7 +101,7 @@ attention_generic_kernel(const TQ* __restrict__ q, TQ* __restrict__ out, const T
 KF_API int kf_attention_generic(const void* q, void* out, int q_dtype, const void* pages, int kv_dtype,
                                 const int* items, const int* positions, const int* row_req, const int* block_table, int table_stride,
                                 int page_size, int nh, int nkv, int d, float scale, float softcap, int window,
-                                int vsplit, int T, cudaStream_t stream) {
+                                int vsplit, int keep_first, int sink, int T, cudaStream_t stream) {
   if (T <= 0) return KF_OK;
   if (d < 1 || d > MAX_D || nkv < 1 || nh % nkv != 0 || page_size < 1 || !kf_head_map_ok(nh, nkv, vsplit)) return KF_ERR_SIZE;
   const long n_work = (long)T * nh;
@@ -101,7 +109,7 @@ KF_API int kf_attention_generic(const void* q, void* out, int q_dtype, const voi
 #define KF_GO(TQ, TKV)                                                                                     \
   kf_launch(attention_generic_kernel<TQ, TKV>, dim3(blocks), dim3(WARPS * 32), 0, stream,                                     \
       (const TQ*)q, (TQ*)out, (const TKV*)pages, items, positions, row_req, block_table, table_stride, page_size, \
-      nh, nkv, d, scale, softcap, window, vsplit, T)
+      nh, nkv, d, scale, softcap, window, vsplit, window > 0 ? keep_first : 0, sink, T)
   if (q_dtype == KF_F32 && kv_dtype == KF_F32) KF_GO(float, float);
   else if (q_dtype == KF_BF16 && kv_dtype == KF_BF16) KF_GO(__nv_bfloat16, __nv_bfloat16);
   else return KF_ERR_DTYPE;

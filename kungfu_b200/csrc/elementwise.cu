@@ -110,6 +110,24 @@ KF_API int kf_add(const float* a, float* x, long n, cudaStream_t stream) {
   return KF_OK;
 }
 
+// out = sa * a + sb * b, 32-bit (the results of two mixers that run side by side on one input).
+__global__ void weighted_sum2_kernel(const float* __restrict__ a, float sa, const float* __restrict__ b, float sb,
+                                     float* __restrict__ out, size_t n) {
+  kf_pdl_trigger();
+  kf_pdl_wait();
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+    out[i] = fmaf(sb, b[i], sa * a[i]);
+}
+
+KF_API int kf_weighted_sum2(const float* a, float sa, const float* b, float sb, float* out, long n, cudaStream_t stream) {
+  if (n <= 0) return KF_OK;
+  const long nb = (n + 255) / 256;
+  kf_launch(weighted_sum2_kernel, dim3((int)(nb > kf_sm_count() * 16 ? kf_sm_count() * 16 : nb)), dim3(256), 0, stream, a, sa,
+            b, sb, out, (size_t)n);
+  KF_CHECK_LAUNCH();
+  return KF_OK;
+}
+
 // dst = (bf16 or f32) copy of src with conversion; used where a 32-bit weight meets bf16 activations.
 template <typename TI, typename TO>
 __global__ void convert_kernel(const TI* __restrict__ src, TO* __restrict__ dst, size_t n) {

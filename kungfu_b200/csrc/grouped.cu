@@ -20,7 +20,8 @@
 // kf_moe_plan: counts the pairs of every expert, lays the pairs out expert by expert (sorted_pair, inverse), and lists
 //   the row tiles of every expert.  One block; the order inside an expert is whatever the atomics give, which no
 //   result depends on (a pair's output row is computed from its own row alone).
-// kf_moe_combine: y[t] = sum_j weight[t, j] * expert_out[inverse[t * top + j]] (+ shared[t]), j ascending.
+// kf_moe_combine: y[t] = sum_j weight[t, j] * expert_out[inverse[t * top + j]] (+ shared[t]), j ascending; without
+//   weights (null) every weight is one (mixtures whose weights went into the experts' inputs).
 #include "mma_tiles.cuh"
 
 constexpr int GM = 64, GN = 64, GK = 16;
@@ -33,6 +34,7 @@ struct KfGroupedArgs {
   const int* tile_group; const int* tile_row0; const int* tile_nrows; const int* n_tiles;
   int T, N, K, gated;
   float limit;
+  const float* row_scale;      // gated products: gate and up of sorted row r are multiplied by row_scale[row_index[r]] first
 };
 
 template <typename TX, typename TW, typename TO, int GATED>
@@ -103,12 +105,13 @@ __global__ void __launch_bounds__(256) grouped_simt_kernel(KfGroupedArgs p) {
   for (int i = 0; i < 4; ++i) {
     const int r = ty * 4 + i;
     if (r >= nrows) continue;
+    const float rs = (GATED && p.row_scale) ? p.row_scale[p.row_index ? p.row_index[r0 + r] : r0 + r] : 1.f;
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const int c = col0 + tx * 4 + j;
       if (c >= N) continue;
-      float v = acc[i][j];
-      if (GATED) v = p.gated == 2 ? v / (1.f + expf(-v)) * acu[i][j] : kf_clamped_swish(v, acu[i][j], p.limit);
+      float v = acc[i][j] * rs;
+      if (GATED) v = p.gated == 2 ? v / (1.f + expf(-v)) * (acu[i][j] * rs) : kf_clamped_swish(v, acu[i][j] * rs, p.limit);
       kf_store(out, (size_t)(r0 + r) * p.ldo + c, v);
     }
   }
@@ -228,9 +231,10 @@ __global__ void __launch_bounds__(256) grouped_mma_kernel(KfGroupedArgs p) {
         const int r = wm * 32 + mi * 16 + gid + (i >= 2 ? 8 : 0);
         const int c = col0 + (GATED ? wn * 16 + nt * 8 : wn * 32 + nt * 8) + 2 * tig + (i & 1);
         if (r >= nrows || c >= N) continue;
+        const float rs = (GATED && p.row_scale) ? p.row_scale[p.row_index ? p.row_index[r0 + r] : r0 + r] : 1.f;
+        const float ga = acc[mi][nt][i] * rs, up = GATED ? acc[mi][nt + 2][i] * rs : 0.f;
         const float v = !GATED ? acc[mi][nt][i]
-                        : (p.gated == 2 ? acc[mi][nt][i] / (1.f + expf(-acc[mi][nt][i])) * acc[mi][nt + 2][i]
-                                        : kf_clamped_swish(acc[mi][nt][i], acc[mi][nt + 2][i], p.limit));
+                        : (p.gated == 2 ? ga / (1.f + expf(-ga)) * up : kf_clamped_swish(ga, up, p.limit));
         kf_store(out, (size_t)(r0 + r) * p.ldo + c, v);
       }
 }
@@ -262,12 +266,12 @@ KF_API int kf_grouped_linear(const void* x, int x_dtype, long x_off, long ldx, l
                              const void* w, int w_dtype, long w_gstride, void* out, int out_dtype, long o_off, long ldo,
                              long o_gstride, const int* tile_group, const int* tile_row0, const int* tile_nrows,
                              const int* n_tiles, int max_tiles, int n_groups, int T, int N, int K, int gated, float limit,
-                             cudaStream_t stream) {
+                             const float* row_scale, cudaStream_t stream) {
   if (N <= 0 || (tile_group ? max_tiles <= 0 : (T <= 0 || n_groups <= 0))) return KF_OK;
   if (K <= 0) return KF_ERR_SIZE;
   const size_t xe = x_dtype == KF_F32 ? 4 : 2, oe = out_dtype == KF_F32 ? 4 : 2;
   KfGroupedArgs p{(const char*)x + x_off * xe, ldx, x_gstride, row_index, row_div > 0 ? row_div : 1, w, w_gstride,
-                  (char*)out + o_off * oe, ldo, o_gstride, tile_group, tile_row0, tile_nrows, n_tiles, T, N, K, gated, limit};
+                  (char*)out + o_off * oe, ldo, o_gstride, tile_group, tile_row0, tile_nrows, n_tiles, T, N, K, gated, limit, row_scale};
   // bfloat16 weights whose rows, groups and bases fall on 16-byte boundaries run on the tensor cores; their row tiles are
   // the plan's 64 rows (GM == TM)
   const bool w_ok = w_dtype == KF_BF16 && K % 8 == 0 && w_gstride % 8 == 0 && ((uintptr_t)w & 15) == 0;
@@ -462,7 +466,7 @@ __global__ void moe_combine_kernel(const float* __restrict__ expert_out, const i
   for (int i = threadIdx.x; i < W; i += blockDim.x) {
     float acc = 0.f;
     for (int j = 0; j < top; ++j)
-      acc = fmaf(weights[(size_t)t * top + j], expert_out[(size_t)inverse[(size_t)t * top + j] * W + i], acc);
+      acc = fmaf(weights ? weights[(size_t)t * top + j] : 1.f, expert_out[(size_t)inverse[(size_t)t * top + j] * W + i], acc);
     if (shared) acc += shared[(size_t)t * W + i];
     y[(size_t)t * W + i] = acc;
   }

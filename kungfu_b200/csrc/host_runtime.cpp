@@ -46,6 +46,7 @@ struct Pool {
 };
 
 struct Group {
+  int keep = 0;                          // tokens at the start of a request that stay readable behind the window
   int window;                            // -1: none
   Pool pool;
   std::vector<int> mirror;               // [max_requests][width]: block tables by state slot, -1 where no page
@@ -184,6 +185,14 @@ KF_HOST_API int kf_cache_cancel_reservation(void* h, int64_t req) {
   return OK;
 }
 
+// the first `keep` tokens of every request stay readable in group g however far its window has moved
+KF_HOST_API int kf_cache_keep_first(void* h, int g, int keep) {
+  Cache* c = (Cache*)h;
+  if (g < 0 || g >= (int)c->groups.size() || keep < 0) return E_COMMIT;
+  c->groups[g].keep = keep;
+  return OK;
+}
+
 // the step that wrote n_new reserved tokens succeeded: advance, and give back the pages a window has passed
 KF_HOST_API int kf_cache_commit(void* h, int64_t req, int n_new) {
   Cache* c = (Cache*)h;
@@ -199,7 +208,8 @@ KF_HOST_API int kf_cache_commit(void* h, int64_t req, int n_new) {
     // a query at position p reads keys >= p - w + 1; the next query sits at r.length
     const int dead = std::min(std::max(0, r.length - w + 1) / c->page_size, r.n_entries[g]);
     int* row = c->row((int)g, r.slot);
-    for (int i = r.first_live[g]; i < dead; ++i) {
+    const int kept = (c->groups[g].keep + c->page_size - 1) / c->page_size;       // pages of the kept first tokens stay
+    for (int i = std::max(r.first_live[g], kept); i < dead; ++i) {
       if (row[i] >= 0) {
         if (!c->groups[g].pool.give_back(row[i])) return E_PAGE_NOT_HELD;
         row[i] = -1;
@@ -479,7 +489,7 @@ struct Sched {
     const int P = cache->page_size;
     for (const Group& g : cache->groups) {
       int need = total;
-      if (g.window >= 0) need = std::min(total, g.window + P + std::min(max_batch_tokens, r.prompt_len));
+      if (g.window >= 0) need = std::min(total, g.window + g.keep + (g.keep ? 2 * P : P) + std::min(max_batch_tokens, r.prompt_len));
       if (ceil_div(need, P) > g.pool.n) return false;
     }
     return true;
@@ -489,7 +499,7 @@ struct Sched {
     std::vector<int> out;
     for (const Group& g : cache->groups) {
       int need = n_pending(r);
-      if (g.window >= 0) need = std::min(need, g.window + P + std::min(max_batch_tokens, n_pending(r)));
+      if (g.window >= 0) need = std::min(need, g.window + g.keep + (g.keep ? 2 * P : P) + std::min(max_batch_tokens, n_pending(r)));
       out.push_back(ceil_div(need, P));
     }
     return out;

@@ -463,14 +463,18 @@ def linear_rope_kv_append(x, wqkv, cos, sin, rot: int, n_heads: int, n_kv_heads:
 
 @_dispatch("paged_attention")
 def paged_attention(q, out, ctx, cache, n_heads: int, n_kv_heads: int, head_dim: int, scale: float, softcap: float,
-                    window: int | None, value_split: int = 0) -> None:
+                    window: int | None, value_split: int = 0, keep_first: int = 0, sink: bool = False) -> None:
     """Causal (optionally windowed, softcapped) attention of every row of the step over its request's pages.
     bfloat16: rows of single-row requests run the split-KV decode kernel, the rest the prefill kernel, when the
     head size has an instance of them; the 32-bit path and other head sizes run the generic kernel.
     value_split = G > 0: every query head over every value head.  `out` has n_heads result heads, q n_heads / G heads and
     the pages G heads (n_kv_heads = G * G counts (key head, value head) pairs): result head h, of pair p = h // r with
-    r = n_heads // n_kv_heads, is query head (p // G) * r + h % r over the keys of head p // G and the values of head p % G."""
+    r = n_heads // n_kv_heads, is query head (p // G) * r + h % r over the keys of head p // G and the values of head p % G.
+    keep_first = K > 0 (with a window): keys 0..K-1 stay visible behind the window, at their true positions.
+    sink: one is added to the softmax's denominator (a key of score 0 that has no value)."""
     T = q.shape[0]
+    keep_first = int(keep_first) if window else 0
+    extras = (keep_first, int(bool(sink)))
     lib = library()
     table = ctx.block_tables[cache.group]
     pages = cache.pages
@@ -478,6 +482,8 @@ def paged_attention(q, out, ctx, cache, n_heads: int, n_kv_heads: int, head_dim:
               _f(scale), _f(softcap), int(window or 0), int(value_split))
     n_dec = getattr(ctx, "n_dec_rows", 0)
     fast = (use_fast_attention and q.dtype == torch.bfloat16 and pages.dtype == torch.bfloat16)
+    if (keep_first or sink) and (value_split or not extras_on_fast_kernels):
+        fast = False
     vs_splits = ctypes.c_int(0)
     own = decode_value_split_kernel if decode_value_split_kernel is not None else value_split >= 3
     if (fast and n_dec > 0 and value_split and softcap == 0.0 and own
@@ -544,9 +550,12 @@ def paged_attention(q, out, ctx, cache, n_heads: int, n_kv_heads: int, head_dim:
         return
     if fast and use_fast_attention:
         note_fallback(f"attention: head size {head_dim} or page size {cache.page_size} has no tensor-core kernel")
-    _check(lib.kf_attention_generic(_p(q), _p(out), _dt(q), _p(pages), _dt(pages), _p(rest), *common, n_rest, _stream()),
+    _check(lib.kf_attention_generic(_p(q), _p(out), _dt(q), _p(pages), _dt(pages), _p(rest), *common, *extras, n_rest, _stream()),
            "attention (generic)")
 
+
+# Whether the tensor-core attention kernels take `keep_first` and `sink`; False sends such launches to the generic kernel.
+extras_on_fast_kernels = False
 
 # Decode rows of value-split attention: True, the kernel that owns all value heads of a tile of query heads; False, the
 # ordinary decode kernels (one block per pair of a key head and a value head); None, the former from three value heads on
@@ -816,10 +825,14 @@ _GATE_ACT = {"silu": 0, "sigmoid": 1}
 
 @_dispatch("head_norm_gate")
 def head_norm_gate(o, weight, eps: float, gate, gate0: int, act: str, out, heads: int, vdim: int) -> None:
-    """out[t, h, :] = o[t, h, :] / rms(o[t, h, :]) * weight * act(gate[t, gate0 + h * vdim + :]); act silu or sigmoid."""
+    """out[t, h, :] = o[t, h, :] / rms(o[t, h, :]) * weight * act(gate[t, gate0 + h * vdim + :]); act silu or sigmoid.
+    `weight` holds vdim numbers (shared by the heads) or heads * vdim (one vector per head)."""
     T = out.shape[0]
+    if weight.numel() not in (vdim, heads * vdim):
+        raise KernelError(f"head_norm_gate: {weight.numel()} weights for {heads} heads of {vdim}")
+    w_stride = vdim if (weight.numel() == heads * vdim and heads > 1) else 0
     _check(library().kf_head_norm_gate(_p(o), _p(weight), _dt(weight), _f(eps), _p(gate), gate.shape[1], int(gate0),
-                                       _GATE_ACT[act], _p(out), _dt(out), heads, vdim, T, _stream()), "head_norm_gate")
+                                       _GATE_ACT[act], _p(out), _dt(out), heads, vdim, T, w_stride, _stream()), "head_norm_gate")
 
 
 @_dispatch("latent_append")
@@ -834,6 +847,92 @@ def latent_append(proj, c0: int, rank: int, weight, eps: float, ctx, cache) -> N
                                       _p(cache.pages), _dt(cache.pages), D, T, _stream()), "latent_append")
 
 
+@_dispatch("latent_rope_append")
+def latent_rope_append(proj, c0: int, rank: int, rot: int, weight, eps: float, cos, sin, interleaved: bool, magnitude: float,
+                       q, q0: int, n_heads: int, q_dim: int, ctx, cache) -> None:
+    """The latent with a rotated key part: c = rms_norm(proj[:, c0:c0 + rank]) * weight goes to the key row and the value
+    row of the single stored head as `latent_append` does; the `rot` columns after it are turned by the rows' angles and
+    filed behind c in the key row (zeros in the value row).  The last `rot` elements of every head of the 32-bit query
+    matrix q [T, q0 + n_heads * (q_dim + rot) ..] are turned in place by the same angles."""
+    T = proj.shape[0]
+    table = ctx.block_tables[cache.group]
+    D = cache.pages.shape[-1]
+    _check(library().kf_latent_rope_append(_p(proj), proj.shape[1], int(c0), int(rank), int(rot), _p(weight), _dt(weight),
+                                           _f(eps), _p(cos), _p(sin), int(bool(interleaved)), _f(magnitude), _p(q), q.shape[1],
+                                           int(q0), int(n_heads), int(q_dim), _p(ctx.positions), _p(ctx.row_req), _p(table),
+                                           table.shape[1], cache.page_size, _p(cache.pages), _dt(cache.pages), D,
+                                           int(cache.writes), T, _stream()), "latent_rope_append")
+
+
+@_dispatch("cols_rmsnorm")
+def cols_rmsnorm(x, c0: int, weight, eps: float, out) -> None:
+    """out[t, :] = rms_norm(x[t, c0:c0 + n]) * weight, n = weight's length; x 32-bit."""
+    T, n = out.shape
+    _check(library().kf_cols_rmsnorm(_p(x), x.shape[1], int(c0), int(n), _p(weight), _dt(weight), _f(eps), _p(out), _dt(out), T,
+                                     _stream()), "cols_rmsnorm")
+
+
+@_dispatch("rownorm_rope_append")
+def rownorm_rope_append(proj, col0: int, bias, q_norm, k_norm, eps: float, cos, sin, rot: int, interleaved: bool,
+                        magnitude: float, n_heads: int, n_kv_heads: int, key_dim: int, value_dim: int, ctx, cache, q_out,
+                        v_mix=None, v_shared=None, v_mode: int = 0) -> None:
+    """From the 32-bit [q | k | v] columns of `proj` to the attention's operands: optional bias, RMS norm of q and of k
+    over ALL their heads at once (weights of n_heads * key_dim and n_kv_heads * key_dim; None: no norm), rotation of the
+    first `rot` elements of every head (interleaved pairs or halves), q into `q_out` [T, n_heads * D], k and v into the
+    pages of `cache`.  v_mode 1: the biased v is also written to `v_shared` [T, n_kv_heads * value_dim] (32-bit);
+    v_mode 2: v <- (1 - v_mix) v + v_mix v_shared before it is filed (`v_mix`: one number on the device)."""
+    T = q_out.shape[0]
+    D = cache.pages.shape[-1]
+    if q_out.shape[1] != n_heads * D:
+        raise KernelError(f"rownorm_rope_append: q rows of {q_out.shape[1]} elements for {n_heads} heads of {D}")
+    table = ctx.block_tables[cache.group]
+    ws = [w for w in (bias, q_norm, k_norm, v_mix) if w is not None]
+    wdt = _dt(ws[0]) if ws else _dt(q_out)
+    if any(_dt(w) != wdt for w in ws):
+        raise KernelError("rownorm_rope_append: bias, norm weights and the mixing number must share one element type")
+    _check(library().kf_rownorm_rope_append(_p(proj), proj.shape[1], int(col0), _p(bias), _p(q_norm), _p(k_norm), wdt, _f(eps),
+                                            _p(cos), _p(sin), int(rot), int(bool(interleaved)), _f(magnitude), n_heads,
+                                            n_kv_heads, key_dim, value_dim, D, _p(v_mix), _p(v_shared), int(v_mode),
+                                            _p(ctx.positions), _p(ctx.row_req), _p(table), table.shape[1], cache.page_size,
+                                            _p(cache.pages), _dt(cache.pages), _p(q_out), _dt(q_out), int(cache.writes), T,
+                                            _stream()), "rownorm_rope_append")
+
+
+@_dispatch("mlstm")
+def mlstm(proj, q0: int, k0: int, v0: int, i0: int, f0: int, bias_i, bias_f, cap: float, memory, norm_state, out, heads: int,
+          dim: int, vdim: int, ctx, writes: bool = True) -> None:
+    """The matrix memory with exponential gates over the rows of every request of the step, from and into `memory`
+    [requests, heads, dim, vdim] and `norm_state` [requests, heads, dim + 4] (n in the first dim places, the running
+    maximum m at place dim), both 32-bit.  q, k, v and the raw gates are column ranges of `proj` (32-bit); q is
+    multiplied by dim^-1/2.  gi = cap tanh((zi + bias_i) / cap), gf = logsigmoid(cap tanh((zf + bias_f) / cap));
+    m' = max(gf + m, gi); S' = exp(gf + m - m') S + exp(gi - m') k v^T, n' likewise with k;
+    out = S'^T q / (max(|n' . q|, exp(-m')) + 1e-6), 32-bit [rows, heads * vdim]."""
+    T = out.shape[0]
+    lib = library()
+    gates = ctx.buf("mlstm_gates", (T * heads * 4,), torch.float32)
+    wdt = _dt(bias_i) if bias_i is not None else F32
+    _check(lib.kf_mlstm_gates(_p(proj), proj.shape[1], int(i0), int(f0), _p(bias_i), _p(bias_f), wdt, _f(cap), _p(norm_state),
+                              norm_state.shape[2], int(dim), _p(gates), heads, ctx.n_reqs, _p(ctx.req_row_start),
+                              _p(ctx.req_n_rows), _p(ctx.req_state_slot), int(writes), _stream()), "mlstm (gates)")
+    _check(lib.kf_mlstm_scan(_p(proj), proj.shape[1], int(q0), int(k0), int(v0), _p(gates), _p(memory), _p(norm_state),
+                             norm_state.shape[2], _p(out), heads, dim, vdim, _f(float(dim) ** -0.5), ctx.n_reqs,
+                             _p(ctx.req_row_start), _p(ctx.req_n_rows), _p(ctx.req_state_slot), int(writes), _stream()),
+           "mlstm (walk)")
+
+
+@_dispatch("weighted_sum2")
+def weighted_sum2(a, sa: float, b, sb: float, out) -> None:
+    """out = sa * a + sb * b (32-bit)."""
+    _check(library().kf_weighted_sum2(_p(a), _f(sa), _p(b), _f(sb), _p(out), ctypes.c_long(out.numel()), _stream()),
+           "weighted_sum2")
+
+
+@_dispatch("convert")
+def convert(src, dst) -> None:
+    """dst = src in dst's element type (32-bit <-> bfloat16)."""
+    _check(library().kf_convert(_p(src), _dt(src), _p(dst), _dt(dst), ctypes.c_long(src.numel()), _stream()), "convert")
+
+
 @_dispatch("repeat_rows")
 def repeat_rows(a, b, parts: int, out_a, out_b) -> None:
     """out_a[t * parts + j] = a[t], out_b likewise (int32): a step's positions and requests for rows that are presented
@@ -843,13 +942,13 @@ def repeat_rows(a, b, parts: int, out_a, out_b) -> None:
 
 
 def _grouped(x, x_off, ldx, x_gstride, row_index, row_div, w, w_gstride, out, o_off, ldo, o_gstride, tiles, max_tiles,
-             n_groups, T, N, K, gated, limit, what):
+             n_groups, T, N, K, gated, limit, what, row_scale=None):
     tg, tr, tn, nt = tiles if tiles is not None else (None, None, None, None)
     L = ctypes.c_long
     _check(library().kf_grouped_linear(_p(x), _dt(x), L(x_off), L(ldx), L(x_gstride), _p(row_index), int(row_div), _p(w),
                                        _dt(w), L(w_gstride), _p(out), _dt(out), L(o_off), L(ldo), L(o_gstride), _p(tg),
                                        _p(tr), _p(tn), _p(nt), int(max_tiles), int(n_groups), int(T), int(N), int(K),
-                                       int(gated), _f(limit), _stream()), what)
+                                       int(gated), _f(limit), _p(row_scale), _stream()), what)
 
 
 def grouped_on_tensor_cores(on: bool) -> None:
@@ -905,11 +1004,14 @@ def moe_plan(ids, n_experts: int, ctx) -> dict:
 
 @_dispatch("moe_linear")
 def moe_linear(x, plan: dict, weight, out, *, gather: bool, gated: bool = False, limit: float = 0.0,
-               activation: str = "clamped_swish") -> None:
+               activation: str = "clamped_swish", row_scale=None) -> None:
     """out[r] = x_r . weight[e(r)]^T for every sorted pair r of the plan, e(r) its expert; weight [E, N (or 2N: gate rows
     then up rows, when gated), K].  `gather`: x holds one row per TOKEN and pair r reads the row of its token; otherwise
     x holds one row per sorted pair.  gated: out = the clamped gated activation of (gate, up) with `limit`, or, with
-    activation 'silu', gate * sigmoid(gate) * up."""
+    activation 'silu', gate * sigmoid(gate) * up.  `row_scale` [T, top] (32-bit, gathered gated products only): gate and
+    up of a pair are multiplied by its number before the activation, which is the expert applied to the scaled input."""
+    if row_scale is not None and not (gated and gather):
+        raise KernelError("moe_linear: a factor per pair is taken by gathered gated products only")
     if gated and activation not in ("clamped_swish", "silu"):
         raise KernelError(f"moe_linear: gated activation {activation!r} is not one of clamped_swish, silu")
     E, NW, K = weight.shape
@@ -918,12 +1020,13 @@ def moe_linear(x, plan: dict, weight, out, *, gather: bool, gated: bool = False,
         raise KernelError(f"moe_linear: x{tuple(x.shape)} weight{tuple(weight.shape)} out{tuple(out.shape)} do not agree")
     tiles = (plan["tile_group"], plan["tile_row0"], plan["tile_nrows"], plan["n_tiles"])
     _grouped(x, 0, K, 0, plan["sorted_pair"] if gather else None, plan["top"] if gather else 1, weight, NW * K, out, 0, N, 0,
-             tiles, plan["max_tiles"], E, plan["pairs"], N, K, (2 if activation == "silu" else 1) if gated else 0, limit, "moe_linear")
+             tiles, plan["max_tiles"], E, plan["pairs"], N, K, (2 if activation == "silu" else 1) if gated else 0, limit, "moe_linear", row_scale=row_scale)
 
 
 @_dispatch("moe_combine")
 def moe_combine(expert_out, plan: dict, weights, shared, y) -> None:
-    """y[t] = sum_j weights[t, j] * expert_out[inverse[t * top + j]] (+ shared[t]), 32-bit, j ascending."""
+    """y[t] = sum_j weights[t, j] * expert_out[inverse[t * top + j]] (+ shared[t]), 32-bit, j ascending; `weights` None:
+    every weight is one."""
     T, W = y.shape
     _check(library().kf_moe_combine(_p(expert_out), _p(plan["inverse"]), _p(weights), _p(shared), _p(y), T, W, plan["top"],
                                     _stream()), "moe_combine")

@@ -236,3 +236,95 @@ class TalkingAttention(Mixer):
 
 
 register_mixer("talking_attention", TalkingAttention)
+
+
+class RowNormAttention(Mixer):
+    """Grouped-query attention whose q and k are normed over the WHOLE projection (all heads of a row at once), with
+    optional extras.  In order, for the input x:
+
+      [q | k | v | g] = x W_in^T (+ bias on q, k, v)            one product over the stacked matrix
+      q <- q / sqrt(mean over all of q's elements of q^2 + eps) * q_norm;  k likewise        (`q_norm`, `k_norm`: weights of
+                                                                 n_heads * key_dim and n_kv_heads * key_dim; None: no norm)
+      q, k <- rotation of the first rotary dims of every head by `position` (its `interleaved` flag chooses the pairing)
+      v <- (1 - lambda) v + lambda v_first                      `v_mix` "mix": v_first = the biased v of the same token in
+                                                                 the layer whose `v_mix` is "first" and whose `v_mix_tag`
+                                                                 is the same; the mixed v is what the pages hold
+      s_j = (q . k_j) * scale; key j is seen from position p iff j <= p and (no window, or p - j < window, or j < keep_first)
+      a = exp(s_j) / (sum exp(s) + 1 if `sink` else sum exp(s))
+      o_h <- o_h * sigmoid(g_h)                                  one gate per head, from the same input x (`gated`)
+      y = o W_o^T
+    Scores, softmax, norms, rotation, mixing and gate are 32-bit."""
+
+    def __init__(self, w_in: torch.Tensor, wo: torch.Tensor, *, n_heads: int, n_kv_heads: int, key_dim: int, value_dim: int,
+                 scale: float, window: int | None = None, keep_first: int = 0, sink: bool = False,
+                 position: PositionEncoding | None = None, bias: torch.Tensor | None = None,
+                 q_norm: torch.Tensor | None = None, k_norm: torch.Tensor | None = None, norm_eps: float = 1e-6,
+                 gated: bool = False, v_mix: str | None = None, v_mix_weight: torch.Tensor | None = None,
+                 v_mix_tag: str = "v_first", out_tag: str = "branch_out"):
+        if n_heads % n_kv_heads:
+            raise ValueError(f"n_heads {n_heads} is not a multiple of n_kv_heads {n_kv_heads}")
+        if v_mix not in (None, "first", "mix"):
+            raise ValueError(f"v_mix {v_mix!r} is not one of None, 'first', 'mix'")
+        self.wo, self.bias = wo, bias
+        self.n_heads, self.n_kv_heads = int(n_heads), int(n_kv_heads)
+        self.key_dim, self.value_dim = int(key_dim), int(value_dim)
+        self.head_dim = ops.attention_head_size(max(self.key_dim, self.value_dim))
+        self.scale = float(scale)
+        self.window = None if window is None else int(window)
+        self.keep_first = int(keep_first) if self.window is not None else 0
+        self.sink = bool(sink)
+        self.position = position
+        self.q_norm, self.k_norm, self.norm_eps = q_norm, k_norm, float(norm_eps)
+        self.gated = bool(gated)
+        self.v_mix, self.v_mix_tag, self.out_tag = v_mix, v_mix_tag, out_tag
+        self.v_mix_weight = v_mix_weight.reshape(-1).contiguous() if (v_mix_weight is not None and v_mix_weight.numel()) else None
+        if v_mix == "mix" and self.v_mix_weight is None and (v_mix_weight is None):
+            raise ValueError("v_mix 'mix' needs the mixing number")
+        self.qkv_width = (self.n_heads + self.n_kv_heads) * self.key_dim + self.n_kv_heads * self.value_dim
+        self.proj_width = self.qkv_width + (self.n_heads if self.gated else 0)
+        self.width = wo.shape[0]
+        if w_in.numel() and w_in.shape[0] != self.proj_width:
+            raise ValueError(f"stacked projection has shape {tuple(w_in.shape)}, expected {self.proj_width} rows")
+        self.w_in = pad_rows(w_in)
+        self.proj_width = max(self.proj_width, self.w_in.shape[0])
+        rot = getattr(position, "rotary_dims", 0) if position is not None else 0
+        if rot > self.key_dim:
+            raise ValueError(f"{rot} rotary dims for keys of {self.key_dim}")
+        ops.check_attention_sizes(self.n_heads, self.n_kv_heads, self.head_dim)
+
+    def state_need(self):
+        return PagedKV(self.n_kv_heads, self.head_dim, self.window, self.keep_first)
+
+    def forward(self, x, ctx, cache):
+        T = x.shape[0]
+        nh, nkv, D = self.n_heads, self.n_kv_heads, self.head_dim
+        proj = ctx.buf("attn_proj", (T, self.proj_width), torch.float32)
+        ops.linear(x, self.w_in, proj)
+        if self.position is not None:
+            cos, sin = self.position.rotation(ctx)
+            rot, interleaved = 2 * cos.shape[1], bool(getattr(self.position, "interleaved", False))
+            mag = float(getattr(self.position, "magnitude", 1.0))
+        else:
+            cos = sin = None
+            rot, interleaved, mag = 0, False, 1.0
+        q = ctx.buf("attn_q", (T, nh * D), ctx.act_dtype)
+        shared, mode = None, 0
+        if self.v_mix is not None:
+            shared = ctx.buf(f"attn_{self.v_mix_tag}", (T, nkv * self.value_dim), torch.float32)
+            mode = 1 if self.v_mix == "first" else 2
+        ops.rownorm_rope_append(proj, 0, self.bias, self.q_norm, self.k_norm, self.norm_eps, cos, sin, rot, interleaved, mag,
+                                nh, nkv, self.key_dim, self.value_dim, ctx, cache, q,
+                                v_mix=self.v_mix_weight if mode == 2 else None, v_shared=shared, v_mode=mode)
+        o = ctx.buf("attn_o", (T, nh * D), ctx.act_dtype)
+        ops.paged_attention(q, o, ctx, cache, nh, nkv, D, self.scale, 0.0, self.window, keep_first=self.keep_first,
+                            sink=self.sink)
+        if self.gated or D != self.value_dim:
+            packed = ctx.buf("attn_gated", (T, nh * self.value_dim), ctx.act_dtype)
+            ops.head_gate(o, proj if self.gated else None, self.qkv_width, nh, self.value_dim, D, packed, ctx)
+            o = packed
+        y = ctx.buf(self.out_tag, (T, self.width), torch.float32)
+        ops.linear(o, self.wo, y)
+        return y
+
+
+register_mixer("row_norm_attention", RowNormAttention)

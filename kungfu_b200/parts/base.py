@@ -25,10 +25,12 @@ import torch
 
 @dataclass(frozen=True)
 class PagedKV:
-    """Keys and values for every past token, in pages; `window` keys at most are ever read when set."""
+    """Keys and values for every past token, in pages; `window` keys at most are ever read when set, plus the first
+    `keep_first` tokens of the request, which stay readable behind the window."""
     n_kv_heads: int
     head_dim: int
     window: int | None = None
+    keep_first: int = 0
 
 
 @dataclass(frozen=True)

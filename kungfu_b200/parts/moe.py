@@ -23,11 +23,15 @@ class RoutedExperts(FeedForward):
     def __init__(self, w_router: torch.Tensor, correction: torch.Tensor | None, w_gate_up: torch.Tensor, w_down: torch.Tensor, *,
                  top: int, scale: float, limit: float, groups: int = 1, keep: int = 1, shared: FeedForward | None = None,
                  score: str = "sigmoid", group_rank: str = "best_two", normalize: bool = True,
-                 activation: str = "clamped_swish"):
+                 activation: str = "clamped_swish", weight_on: str = "output"):
         """w_gate_up [E, 2 ff, width] (gate rows, then up rows, per expert), w_down [E, width, ff].
         Other mixtures of the same shape: `score` 'softmax' (scores = the softmax of z over all experts), `group_rank`
         'best' (a group scores its largest member), `normalize` False (the winners keep their scores as weights, times
-        `scale`), `activation` 'silu' (experts W_down [silu(g) u])."""
+        `scale`), `activation` 'silu' (experts W_down [silu(g) u]), `weight_on` 'input' (y = sum of expert_e(weight_e x):
+        the weight multiplies what the expert reads, i.e. its gate and up rows before the activation, not its result)."""
+        if weight_on not in ("output", "input"):
+            raise ValueError(f"weight_on {weight_on!r} is not one of output, input")
+        self.weight_on = weight_on
         if score not in ("sigmoid", "softmax") or group_rank not in ("best_two", "best") or activation not in ("clamped_swish", "silu"):
             raise ValueError(f"score {score!r}, group_rank {group_rank!r} or activation {activation!r} is not known")
         self.score, self.group_rank, self.normalize, self.activation = score, group_rank, bool(normalize), activation
@@ -58,12 +62,14 @@ class RoutedExperts(FeedForward):
                       group_rank=self.group_rank, normalize=self.normalize)
         plan = ops.moe_plan(ids, E, ctx)
         h = ctx.buf("moe_h", (T * top, self.inner), ctx.act_dtype)
-        ops.moe_linear(x, plan, self.w_gate_up, h, gather=True, gated=True, limit=self.limit, activation=self.activation)
+        on_input = self.weight_on == "input"
+        ops.moe_linear(x, plan, self.w_gate_up, h, gather=True, gated=True, limit=self.limit, activation=self.activation,
+                       row_scale=wts if on_input else None)
         eo = ctx.buf("moe_expert_out", (T * top, self.width), torch.float32)
         ops.moe_linear(h, plan, self.w_down, eo, gather=False)
         sh = self.shared.forward(x, ctx) if self.shared is not None else None
         y = ctx.buf("ffn_out", (T, self.width), torch.float32)
-        ops.moe_combine(eo, plan, wts, sh, y)
+        ops.moe_combine(eo, plan, None if on_input else wts, sh, y)
         return y
 
 

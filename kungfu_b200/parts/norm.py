@@ -83,3 +83,23 @@ class GroupRmsNorm(Norm):
 
 
 register_norm("group_rms", GroupRmsNorm)
+
+
+class NoNorm(Norm):
+    """The place of a norm in a block whose sublayers read the residual stream itself: the rows pass unchanged, in the
+    element type the sublayer's products take (the residual's own rows when that is 32-bit)."""
+
+    def __init__(self, width: int):
+        self.width = int(width)
+
+    def forward(self, x, ctx, out_dtype, rows=None):
+        if rows is not None:
+            raise NotImplementedError("NoNorm passes whole steps only")
+        if out_dtype == x.dtype:
+            return x
+        out = ctx.buf("norm_out", (x.shape[0], self.width), out_dtype)
+        ops.convert(x, out)
+        return out
+
+
+register_norm("none", NoNorm)

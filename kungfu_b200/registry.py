@@ -61,6 +61,9 @@ def _register_builtin() -> None:
     from .config.pimodra import PimodraConfig
     from .models import pimodra
     register("Pimodra", PimodraConfig.from_dict, pimodra.build, pimodra.tensor_specs, replace=True)
+    from .config.nukelix import NukelixConfig
+    from .models import nukelix
+    register("Nukelix", NukelixConfig.from_dict, nukelix.build, nukelix.tensor_specs, replace=True)
 
 
 _register_builtin()
