@@ -151,7 +151,7 @@ def write_safetensors(path: str, tensors: dict[str, torch.Tensor], metadata: dic
         t = t.detach().cpu().contiguous()
         if t.dtype not in _TAG_OF:
             raise WeightFileError(f"tensor '{name}': dtype {t.dtype} cannot be stored")
-        raw = t.view(torch.uint8).reshape(-1) if t.numel() else torch.empty(0, dtype=torch.uint8)
+        raw = t.reshape(-1).view(torch.uint8) if t.numel() else torch.empty(0, dtype=torch.uint8)   # also a tensor of no axes
         if t.dtype == torch.bfloat16:
             raw = t.view(torch.int16).reshape(-1).view(torch.uint8)
         n = raw.numel()

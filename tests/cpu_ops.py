@@ -97,7 +97,7 @@ class CpuOps:
             cache.pages[page, 0, :, pos % P, :] = k[t].to(cache.pages.dtype)
             cache.pages[page, 1, :, pos % P, :] = v[t].to(cache.pages.dtype)
 
-    def paged_attention(self, q, out, ctx, cache, nh, nkv, d, scale, softcap, window, value_split=0):
+    def paged_attention(self, q, out, ctx, cache, nh, nkv, d, scale, softcap, window, value_split=0, keep_first=0, sink=False):
         T = q.shape[0]
         table = ctx.block_tables[cache.group]
         P = cache.page_size
@@ -110,7 +110,7 @@ class CpuOps:
                 continue
             pos = int(ctx.positions[t])
             lo = max(0, pos - window + 1) if window else 0
-            js = list(range(lo, pos + 1))
+            js = list(range(0, min(keep_first, lo) if window else 0)) + list(range(lo, pos + 1))
             pages = [int(table[r, j // P]) for j in js]
             assert all(p >= 0 for p in pages), f"row {t} reads a page that was given back"
             slots = [j % P for j in js]
@@ -127,7 +127,10 @@ class CpuOps:
                 s = (K[:, kh] @ qt[qh]) * scale
                 if softcap > 0:
                     s = softcap * torch.tanh(s / softcap)
-                p = torch.softmax(s, dim=0)
+                if sink:                      # one more term, exp(0), in the denominator
+                    p = torch.softmax(torch.cat([s, s.new_zeros(1)]), dim=0)[:-1]
+                else:
+                    p = torch.softmax(s, dim=0)
                 out[t, h * d:(h + 1) * d] = (p @ V[:, vh]).to(out.dtype)
 
     # ---- short convolution, q|k|v preparation, state-space scan (restatements of what the kernels of the same names do) ----------------
@@ -299,7 +302,8 @@ class CpuOps:
     def head_norm_gate(self, o, weight, eps, gate, gate0, act, out, heads, vdim):
         T = out.shape[0]
         y = o[:T].float().view(T, heads, vdim)
-        y = y * torch.rsqrt(y.pow(2).mean(-1, keepdim=True) + eps) * weight.float()[None, None, :]
+        w = weight.float().view(heads, vdim)[None] if weight.numel() == heads * vdim else weight.float()[None, None, :]
+        y = y * torch.rsqrt(y.pow(2).mean(-1, keepdim=True) + eps) * w
         z = gate[:T, gate0:gate0 + heads * vdim].float().view(T, heads, vdim)
         y = y * (z * torch.sigmoid(z) if act == "silu" else torch.sigmoid(z))
         out.copy_(torch.nan_to_num(y).reshape(T, heads * vdim).to(out.dtype))
@@ -428,6 +432,125 @@ class CpuOps:
         y[ctx.row_req[:T] < 0] = 0
         out.copy_(y.to(out.dtype))
 
+    @staticmethod
+    def _turn(y, cos, sin, rot, interleaved, magnitude):
+        """y [T, heads, n]: the first `rot` elements of every head turned in place by the rows' angles."""
+        if not rot:
+            return
+        c, s_ = cos[:, None, :] * magnitude, sin[:, None, :] * magnitude
+        if interleaved:
+            a, b = y[..., 0:rot:2].clone(), y[..., 1:rot:2].clone()
+            y[..., 0:rot:2] = a * c - b * s_
+            y[..., 1:rot:2] = b * c + a * s_
+        else:
+            a, b = y[..., :rot // 2].clone(), y[..., rot // 2:rot].clone()
+            y[..., :rot // 2] = a * c - b * s_
+            y[..., rot // 2:rot] = b * c + a * s_
+
+    def rownorm_rope_append(self, proj, col0, bias, q_norm, k_norm, eps, cos, sin, rot, interleaved, magnitude, nh, nkv, dk, dv,
+                            ctx, cache, q_out, v_mix=None, v_shared=None, v_mode=0):
+        T = q_out.shape[0]
+        D = cache.pages.shape[-1]
+        C = (nh + nkv) * dk + nkv * dv
+        x = proj[:T, col0:col0 + C].float()
+        if bias is not None:
+            x = x + bias.float()[None, :]
+        q, k, v = x[:, :nh * dk].clone(), x[:, nh * dk:(nh + nkv) * dk].clone(), x[:, (nh + nkv) * dk:].clone()
+        if q_norm is not None:
+            q = q * torch.rsqrt(q.pow(2).mean(-1, keepdim=True) + eps) * q_norm.float()
+        if k_norm is not None:
+            k = k * torch.rsqrt(k.pow(2).mean(-1, keepdim=True) + eps) * k_norm.float()
+        q, k, v = q.reshape(T, nh, dk), k.reshape(T, nkv, dk), v.reshape(T, nkv, dv)
+        self._turn(q, cos, sin, rot, interleaved, magnitude)
+        self._turn(k, cos, sin, rot, interleaved, magnitude)
+        live = ctx.row_req[:T] >= 0
+        if v_mode == 1 and cache.writes:
+            v_shared[:T][live] = v.reshape(T, nkv * dv)[live]
+        elif v_mode == 2:
+            lam = float(v_mix.reshape(-1)[0])
+            v = (1.0 - lam) * v + lam * v_shared[:T].float().view(T, nkv, dv)
+        qp = torch.zeros(T, nh, D)
+        qp[:, :, :dk] = q
+        qp[~live] = 0
+        q_out.copy_(qp.reshape(T, nh * D).to(q_out.dtype))
+        if not cache.writes:
+            return
+        table = ctx.block_tables[cache.group]
+        P = cache.page_size
+        for t in range(T):
+            r = int(ctx.row_req[t])
+            if r < 0:
+                continue
+            pos = int(ctx.positions[t])
+            page = int(table[r, pos // P])
+            assert page >= 0
+            cache.pages[page, :, :, pos % P, :] = 0
+            cache.pages[page, 0, :, pos % P, :dk] = k[t].to(cache.pages.dtype)
+            cache.pages[page, 1, :, pos % P, :dv] = v[t].to(cache.pages.dtype)
+
+    def cols_rmsnorm(self, x, c0, weight, eps, out):
+        T, n = out.shape
+        c = x[:T, c0:c0 + n].float()
+        out.copy_((c * torch.rsqrt(c.pow(2).mean(-1, keepdim=True) + eps) * weight.float()).to(out.dtype))
+
+    def latent_rope_append(self, proj, c0, rank, rot, weight, eps, cos, sin, interleaved, magnitude, q, q0, n_heads, q_dim, ctx, cache):
+        T = proj.shape[0]
+        live = ctx.row_req[:T] >= 0
+        heads = q[:T, q0:q0 + n_heads * (q_dim + rot)].view(T, n_heads, q_dim + rot)
+        part = heads[..., q_dim:].clone()
+        self._turn(part, cos[:T], sin[:T], rot, interleaved, magnitude)
+        heads[..., q_dim:][live] = part[live]
+        if not cache.writes:
+            return
+        table = ctx.block_tables[cache.group]
+        D = cache.pages.shape[-1]
+        kr = proj[:T, c0 + rank:c0 + rank + rot].float().reshape(T, 1, rot).clone()
+        self._turn(kr, cos[:T], sin[:T], rot, interleaved, magnitude)
+        for t in range(T):
+            req = int(ctx.row_req[t])
+            if req < 0:
+                continue
+            c = proj[t, c0:c0 + rank].float()
+            c = c * torch.rsqrt(c.pow(2).mean() + eps) * weight.float()
+            pos = int(ctx.positions[t])
+            page = int(table[req, pos // cache.page_size])
+            key, val = torch.zeros(D), torch.zeros(D)
+            key[:rank] = val[:rank] = c
+            key[rank:rank + rot] = kr[t, 0]
+            cache.pages[page, 0, 0, pos % cache.page_size] = key.to(cache.pages.dtype)
+            cache.pages[page, 1, 0, pos % cache.page_size] = val.to(cache.pages.dtype)
+
+    def mlstm(self, proj, q0, k0, v0, i0, f0, bias_i, bias_f, cap, memory, norm_state, out, heads, dim, vdim, ctx, writes=True):
+        H, d, dv = heads, dim, vdim
+        for r in range(ctx.n_reqs):
+            n, row0, slot = int(ctx.req_n_rows[r]), int(ctx.req_row_start[r]), int(ctx.req_state_slot[r])
+            if n <= 0 or slot < 0:
+                continue
+            S, nn, m = memory[slot].float().clone(), norm_state[slot, :, :d].float().clone(), norm_state[slot, :, d].float().clone()
+            for t in range(row0, row0 + n):
+                x = proj[t].float()
+                gi = cap * torch.tanh((x[i0:i0 + H] + bias_i.float()) / cap)
+                gf = torch.nn.functional.logsigmoid(cap * torch.tanh((x[f0:f0 + H] + bias_f.float()) / cap))
+                m_new = torch.maximum(gf + m, gi)
+                keep, take = torch.exp(gf + m - m_new), torch.exp(gi - m_new)
+                q = x[q0:q0 + H * d].view(H, d) * d ** -0.5
+                k, v = x[k0:k0 + H * d].view(H, d), x[v0:v0 + H * dv].view(H, dv)
+                S = keep[:, None, None] * S + take[:, None, None] * k[:, :, None] * v[:, None, :]
+                nn = keep[:, None] * nn + take[:, None] * k
+                m = m_new
+                den = torch.maximum((nn * q).sum(-1).abs(), torch.exp(-m)) + 1e-6
+                out[t] = (torch.einsum("hdv,hd->hv", S, q) / den[:, None]).reshape(H * dv)
+            if writes:
+                memory[slot] = S
+                norm_state[slot, :, :d] = nn
+                norm_state[slot, :, d] = m
+
+    def weighted_sum2(self, a, sa, b, sb, out):
+        out.copy_(sa * a + sb * b)
+
+    def convert(self, src, dst):
+        dst.copy_(src.to(dst.dtype))
+
     def moe_plan(self, ids, n_experts, ctx):
         T, top = ids.shape
         flat = ids.reshape(-1).long()
@@ -437,12 +560,14 @@ class CpuOps:
         return {"pairs": T * top, "top": top, "sorted_pair": order.to(torch.int32), "inverse": inverse.to(torch.int32),
                 "expert_of_sorted": flat[order]}
 
-    def moe_linear(self, x, plan, weight, out, *, gather, gated=False, limit=0.0, activation="clamped_swish"):
+    def moe_linear(self, x, plan, weight, out, *, gather, gated=False, limit=0.0, activation="clamped_swish", row_scale=None):
         top = plan["top"]
         for r in range(plan["pairs"]):
             e = int(plan["expert_of_sorted"][r])
             row = x[int(plan["sorted_pair"][r]) // top] if gather else x[r]
             y = weight[e].float() @ row.float()
+            if row_scale is not None:
+                y = y * row_scale.reshape(-1)[int(plan["sorted_pair"][r])]
             if gated:
                 N = y.shape[0] // 2
                 y = y[:N] * torch.sigmoid(y[:N]) * y[N:] if activation == "silu" else self._clamped(y[:N], y[N:], limit)
@@ -452,7 +577,7 @@ class CpuOps:
         T, W = y.shape
         top = plan["top"]
         rows = expert_out[plan["inverse"].long()].view(T, top, W)
-        acc = (rows * weights[:, :, None]).sum(1)
+        acc = (rows * weights[:, :, None]).sum(1) if weights is not None else rows.sum(1)
         y.copy_(acc + (shared if shared is not None else 0.0))
 
     def scale_add_rmsnorm(self, a, scale, x, *, next_weight=None, next_eps=0.0, next_plus_one=False, next_out=None, copy_out=None):
