@@ -366,8 +366,9 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const float* __restr
                        const float* __restrict__ sin_t, int rot, int write_kv, __nv_bfloat16* pages,
                        const int* __restrict__ items, int n_items, const int* __restrict__ positions,
                        const int* __restrict__ row_req, const int* __restrict__ table, int table_stride, int page_size,
-                       int nh, int nkv, float scale, float softcap, int window, int vsplit, int n_splits,
-                       float* __restrict__ partial, int* __restrict__ counters, __nv_bfloat16* __restrict__ out) {
+                       int nh, int nkv, float scale, float softcap, int window, int vsplit, int keep_first, int sink,
+                       int n_splits, float* __restrict__ partial, int* __restrict__ counters,
+                       __nv_bfloat16* __restrict__ out) {
   using namespace kf_mma;
   kf_pdl_trigger();
   constexpr int CH = D / 8;
@@ -400,10 +401,14 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const float* __restr
   }
   const int pos = positions[t];
   const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
-  const int n_keys = pos + 1 - lo;
+  // Kept first tokens: keys [0, kept) are seen behind the window.  The keys are walked by a running index u in
+  // [lo_v, pos]: u >= lo is key u itself, u in [lo_v, lo) is key u - lo_v, so the walk below does not know of the gap.
+  const int kept = window > 0 ? min(keep_first, lo) : 0;
+  const int lo_v = lo - kept;
+  const int n_keys = pos + 1 - lo_v;
   int per = (n_keys + n_splits - 1) / n_splits;
   per = (per + 63) & ~63;
-  const int k_begin = lo + split * per;
+  const int k_begin = lo_v + split * per;
   const int k_end = min(pos + 1, k_begin + per);
   const int n_tiles = k_end > k_begin ? (k_end - k_begin + DM_KEYS - 1) / DM_KEYS : 0;
   // the tile that holds the row's own key: an earlier kernel of this step writes that key (or this block does)
@@ -425,8 +430,9 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const float* __restr
     // lanes 0..15 look up the row of key j0 + lane; everyone fetches a row's base by shuffle
     row_base = -1;
     if (lane < DM_KEYS) {
-      const int j = j0 + lane;
-      if (j < k_end) {
+      const int u = j0 + lane;
+      if (u < k_end) {
+        const int j = u >= lo ? u : u - lo_v;
         const int page = tab[j / page_size];
         if (page >= 0) row_base = ((long)page * 2 * hm.n_stored + hm.key) * (long)head_stride + (long)(j % page_size) * D;
       }
@@ -645,9 +651,11 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const float* __restr
   const size_t rec_base = (((size_t)t * nh + h_first) * n_splits + split) * PSTRIDE;
   for (int e = tid; e < G * D; e += blockDim.x) {
     const int h = e / D, i = e - h * D;
-    float m = -INFINITY;
+    // the sink (a key of score 0 without a value) joins the first split like one more warp: maximum 0, sum 1, no row
+    const bool sink_here = sink && split == 0;
+    float m = sink_here ? 0.f : -INFINITY;
     for (int w = 0; w < DM_WARPS; ++w) m = fmaxf(m, sm_ml[w][h][0]);
-    float l = 0.f, a = 0.f;
+    float l = sink_here ? exp2f(-m) : 0.f, a = 0.f;
     for (int w = 0; w < DM_WARPS; ++w) {
       const float mw = sm_ml[w][h][0];
       const float c = (mw == -INFINITY) ? 0.f : exp2f(mw - m);
@@ -695,13 +703,14 @@ template <int D>
 int launch_decode_mma(const float* qkv, const float* cos_t, const float* sin_t, int rot, int write_kv,
                       const void* q, const void* pages, const int* items, int n_items, const int* positions,
                       const int* row_req, const int* table, int table_stride, int page_size, int nh, int nkv, float scale,
-                      float softcap, int window, int vsplit, int n_splits, float* partial, int* counters, void* out, cudaStream_t stream) {
+                      float softcap, int window, int vsplit, int keep_first, int sink, int n_splits, float* partial, int* counters,
+                      void* out, cudaStream_t stream) {
   const size_t smem = (size_t)(16 * D + DM_WARPS * DM_BUFS * DM_KEYS * D) * 2;
   if (decode_mma_blocks_per_sm<D>() < 1) return KF_ERR_SETUP;
   kf_launch(attn_decode_mma_kernel<D>, dim3(n_items * nkv, n_splits), dim3(DM_WARPS * 32), smem, stream,
             (const __nv_bfloat16*)q, qkv, cos_t, sin_t, rot, write_kv, (__nv_bfloat16*)const_cast<void*>(pages), items, n_items,
-            positions, row_req, table, table_stride, page_size, nh, nkv, scale, softcap, window, vsplit, n_splits, partial, counters,
-            (__nv_bfloat16*)out);
+            positions, row_req, table, table_stride, page_size, nh, nkv, scale, softcap, window, vsplit, keep_first, sink, n_splits,
+            partial, counters, (__nv_bfloat16*)out);
   KF_CHECK_LAUNCH();
   return KF_OK;
 }
@@ -780,14 +789,17 @@ KF_API int kf_attention_decode_plan(int n_items, int nh, int nkv, int d, int max
 KF_API int kf_attention_decode(const void* q, void* out, const void* pages, const int* items, int n_items,
                                const int* positions, const int* row_req, const int* table, int table_stride,
                                int page_size, int nh, int nkv, int d, float scale, float softcap, int window, int vsplit,
-                               int ht, int n_splits, float* partial, int* counters, cudaStream_t stream) {
+                               int ht, int n_splits, float* partial, int* counters, int keep_first, int sink,
+                               cudaStream_t stream) {
   if (n_items <= 0) return KF_OK;
+  if ((keep_first > 0 || sink) && ht != 0) return KF_ERR_SIZE;     // kept first tokens and the sink: tensor-core variant only
+  if (window <= 0) keep_first = 0;
   if (nkv < 1 || nh % nkv != 0 || page_size < 1 || n_splits < 1 || !kf_head_map_ok(nh, nkv, vsplit)) return KF_ERR_SIZE;
   if (n_splits > 1 && (!partial || !counters)) return KF_ERR_SIZE;
   if (n_splits > MERGE_MAX_SPLITS || ht > MERGE_MAX_HEADS) return KF_ERR_SIZE;
   if (ht == 0) {                                     // tensor-core variant
     if (nh / nkv > 16) return KF_ERR_SIZE;
-#define KF_MMA_ARGS nullptr, nullptr, nullptr, 0, 0, q, pages, items, n_items, positions, row_req, table, table_stride, page_size, nh, nkv, scale, softcap, window, vsplit, n_splits, partial, counters, out, stream
+#define KF_MMA_ARGS nullptr, nullptr, nullptr, 0, 0, q, pages, items, n_items, positions, row_req, table, table_stride, page_size, nh, nkv, scale, softcap, window, vsplit, keep_first, sink, n_splits, partial, counters, out, stream
     switch (d) {
       case 16: return launch_decode_mma<16>(KF_MMA_ARGS);
       case 32: return launch_decode_mma<32>(KF_MMA_ARGS);
@@ -823,7 +835,7 @@ KF_API int kf_attention_decode_fused(const float* qkv, const float* cos_t, const
   if (rot < 0 || rot > d || (rot & 1) || (rot > 0 && (!cos_t || !sin_t))) return KF_ERR_SIZE;
   if (n_splits > 1 && (!partial || !counters)) return KF_ERR_SIZE;
   if (n_splits > MERGE_MAX_SPLITS) return KF_ERR_SIZE;
-#define KF_MMA_ARGS qkv, cos_t, sin_t, rot, write_kv, nullptr, pages, items, n_items, positions, row_req, table, table_stride, page_size, nh, nkv, scale, softcap, window, 0, n_splits, partial, counters, out, stream
+#define KF_MMA_ARGS qkv, cos_t, sin_t, rot, write_kv, nullptr, pages, items, n_items, positions, row_req, table, table_stride, page_size, nh, nkv, scale, softcap, window, 0, 0, 0, n_splits, partial, counters, out, stream
   switch (d) {
     case 16: return launch_decode_mma<16>(KF_MMA_ARGS);
     case 32: return launch_decode_mma<32>(KF_MMA_ARGS);
@@ -906,5 +918,5 @@ KF_API int kf_attention_decode_static(const void* q, void* out, const void* page
     }
   }
   return kf_attention_decode(q, out, pages, nullptr, n_rows, positions, row_req, table, table_stride, page_size, nh, nkv,
-                             d, scale, softcap, window, 0, ht, splits, partial, counters, stream);
+                             d, scale, softcap, window, 0, ht, splits, partial, counters, 0, 0, stream);
 }

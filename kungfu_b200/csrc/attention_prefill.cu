@@ -27,7 +27,8 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
                     const int* __restrict__ tile_row0, const int* __restrict__ tile_nrows,
                     const int* __restrict__ positions, const int* __restrict__ row_req,
                     const int* __restrict__ table, int table_stride, int page_size, int nh, int nkv,
-                    float scale, float softcap, int window, int vsplit, __nv_bfloat16* __restrict__ out) {
+                    float scale, float softcap, int window, int vsplit, int keep_first, int sink,
+                    __nv_bfloat16* __restrict__ out) {
   kf_pdl_trigger();
   kf_pdl_wait();
   constexpr int CH = D / 8;                       // 16-byte chunks per row
@@ -50,7 +51,11 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
   const int pos_last = pos0 + nrows - 1;
   const int lo = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;
   const int kt_begin = (lo / BNK) * BNK;
-  const int n_ktiles = (pos_last - kt_begin) / BNK + 1;
+  // kept first tokens that lie before the first tile of the window: their tiles are walked first (the mask below lets a
+  // row see key j < keep_first wherever its window stands)
+  const int n_kept_tiles = (window > 0 && keep_first > 0) ? (min(keep_first, kt_begin) + BNK - 1) / BNK : 0;
+  const int n_ktiles = n_kept_tiles + (pos_last - kt_begin) / BNK + 1;
+  auto first_key = [&](int it) { return it < n_kept_tiles ? it * BNK : kt_begin + (it - n_kept_tiles) * BNK; };
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, tq = lane & 3;
   const int* tab = table + (size_t)req * table_stride;
@@ -79,20 +84,23 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
       cp_async16(tile_ptr<D>(dv, r, c), src + v_off, ok);
     }
   };
-  load_kv(kt_begin, 0);
+  load_kv(first_key(0), 0);
   cp_async_commit();
 
   float o_acc[NT_O][4];
 #pragma unroll
   for (int n = 0; n < NT_O; ++n) { o_acc[n][0] = o_acc[n][1] = o_acc[n][2] = o_acc[n][3] = 0.f; }
-  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+  // the sink (a key of score 0 without a value): the walk starts from maximum 0 and sum 1 (the sums are kept per lane of
+  // a quad and added at the end, so one lane holds the 1)
+  float m_run[2] = {sink ? 0.f : -INFINITY, sink ? 0.f : -INFINITY};
+  float l_run[2] = {(sink && (lane & 3) == 0) ? 1.f : 0.f, (sink && (lane & 3) == 0) ? 1.f : 0.f};
   const int prow[2] = {pos0 + warp * 16 + g, pos0 + warp * 16 + g + 8};   // positions of this thread's two rows
   const float cap2 = softcap > 0.f ? 2.f * LOG2E / softcap : 0.f;
 
   for (int it = 0; it < n_ktiles; ++it) {
     const int stage = it & 1;
-    const int kt = kt_begin + it * BNK;
-    if (it + 1 < n_ktiles) load_kv(kt + BNK, stage ^ 1);
+    const int kt = first_key(it);
+    if (it + 1 < n_ktiles) load_kv(first_key(it + 1), stage ^ 1);
     cp_async_commit();
     cp_async_wait<1>();
     __syncthreads();
@@ -129,7 +137,7 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
           const float ex = exp2f(s * cap2);
           s = softcap * (1.f - __fdividef(2.f, ex + 1.f));
         }
-        const bool seen = j <= prow[r] && (window <= 0 || prow[r] - j < window);
+        const bool seen = j <= prow[r] && (window <= 0 || prow[r] - j < window || j < keep_first);
         s = seen ? s * LOG2E : -INFINITY;
         s_acc[n][e] = s;
         m_new[r] = fmaxf(m_new[r], s);
@@ -204,7 +212,8 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
 template <int D, int BNK>
 int launch_prefill(const void* q, void* out, const void* pages, const int* tile_row0, const int* tile_nrows, int n_tiles,
                    const int* positions, const int* row_req, const int* table, int table_stride, int page_size,
-                   int nh, int nkv, float scale, float softcap, int window, int vsplit, cudaStream_t stream) {
+                   int nh, int nkv, float scale, float softcap, int window, int vsplit, int keep_first, int sink,
+                   cudaStream_t stream) {
   const size_t smem = (size_t)(BM * D + 4 * BNK * D) * 2;
   static bool configured = false;
   if (!configured) {
@@ -216,7 +225,7 @@ int launch_prefill(const void* q, void* out, const void* pages, const int* tile_
   }
   kf_launch(attn_prefill_kernel<D, BNK>, dim3(n_tiles, nh), dim3(PF_WARPS * 32), smem, stream, 
       (const __nv_bfloat16*)q, (const __nv_bfloat16*)pages, tile_row0, tile_nrows, positions, row_req, table, table_stride,
-      page_size, nh, nkv, scale, softcap, window, vsplit, (__nv_bfloat16*)out);
+      page_size, nh, nkv, scale, softcap, window, vsplit, window > 0 ? keep_first : 0, sink, (__nv_bfloat16*)out);
   KF_CHECK_LAUNCH();
   return KF_OK;
 }
@@ -231,10 +240,10 @@ KF_API int kf_attention_prefill_tile_rows() { return BM; }
 KF_API int kf_attention_prefill(const void* q, void* out, const void* pages, const int* tile_row0, const int* tile_nrows,
                                 int n_tiles, const int* positions, const int* row_req, const int* table, int table_stride,
                                 int page_size, int nh, int nkv, int d, float scale, float softcap, int window, int vsplit,
-                                cudaStream_t stream) {
+                                int keep_first, int sink, cudaStream_t stream) {
   if (n_tiles <= 0) return KF_OK;
   if (nkv < 1 || nh % nkv != 0 || page_size < 1 || !kf_head_map_ok(nh, nkv, vsplit)) return KF_ERR_SIZE;
-#define KF_ARGS q, out, pages, tile_row0, tile_nrows, n_tiles, positions, row_req, table, table_stride, page_size, nh, nkv, scale, softcap, window, vsplit, stream
+#define KF_ARGS q, out, pages, tile_row0, tile_nrows, n_tiles, positions, row_req, table, table_stride, page_size, nh, nkv, scale, softcap, window, vsplit, keep_first, sink, stream
   switch (d) {
     case 16: return launch_prefill<16, 64>(KF_ARGS);
     case 32: return launch_prefill<32, 64>(KF_ARGS);

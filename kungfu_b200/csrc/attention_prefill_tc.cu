@@ -187,12 +187,18 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const float* v) {
 // The 64-key tiles a tile of query rows reads (and its first key), and into how many runs they are cut: `n_parts` runs for
 // every tile when `run_tiles` is 0; otherwise as many runs of at most `run_tiles` key tiles as the tile needs, at most
 // n_parts (short tiles then stay whole and write their rows themselves, long ones are shared between blocks).
+// With kept first tokens (keys 0..keep_first-1 stay visible behind the window) the tiles of those keys that lie before
+// the window's first tile are walked first: `*n_kept` of them, tile i of the walk starting at key_of_tile(i, ...).
 __device__ __forceinline__ int tile_key_tiles(int row0, int nrows, const int* positions, const int* row_req, int window,
-                                              int* kt_first) {
+                                              int keep_first, int* kt_first, int* n_kept) {
   const int pos0 = positions[row0];
   const int lo = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;
   *kt_first = (lo / BKV) * BKV;
-  return (row_req[row0] < 0 || nrows <= 0) ? 0 : (pos0 + nrows - 1 - *kt_first) / BKV + 1;   // padding, or a tile without rows
+  *n_kept = (window > 0 && keep_first > 0) ? (min(keep_first, *kt_first) + BKV - 1) / BKV : 0;
+  return (row_req[row0] < 0 || nrows <= 0) ? 0 : *n_kept + (pos0 + nrows - 1 - *kt_first) / BKV + 1;   // padding, or a tile without rows
+}
+__device__ __forceinline__ int key_of_tile(int i, int kt_first, int n_kept) {
+  return i < n_kept ? i * BKV : kt_first + (i - n_kept) * BKV;
 }
 __device__ __forceinline__ int tile_runs(int n_key_tiles, int n_parts, int run_tiles) {
   if (n_parts <= 1) return 1;
@@ -207,8 +213,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
                        const int* __restrict__ tile_row0, const int* __restrict__ tile_nrows,
                        const int* __restrict__ positions, const int* __restrict__ row_req,
                        const int* __restrict__ table, int table_stride, int page_size, int nh, int nkv,
-                       float scale, float softcap, int window, int vsplit, __nv_bfloat16* __restrict__ out,
-                       int* __restrict__ error_flag, int n_parts, int run_tiles, float* __restrict__ partial) {
+                       float scale, float softcap, int window, int vsplit, int keep_first, int sink,
+                       __nv_bfloat16* __restrict__ out, int* __restrict__ error_flag, int n_parts, int run_tiles,
+                       float* __restrict__ partial) {
   constexpr int NSUB = D / 64;                            // 64-element sub-tiles along the head dimension
   constexpr int Q_BYTES = BMQ * D * 2;
   constexpr int KV_BYTES = BKV * D * 2;                   // one K tile (or one V tile)
@@ -279,12 +286,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
   // the step's integers were written before the step's first kernel: read before the grid dependency is waited for
   const int req = row_req[row0];
   const int pos0 = positions[row0];
-  int kt_first;
-  const int n_tiles_all = tile_key_tiles(row0, nrows, positions, row_req, window, &kt_first);
+  int kt_first, n_kept;
+  const int n_tiles_all = tile_key_tiles(row0, nrows, positions, row_req, window, keep_first, &kt_first, &n_kept);
   const int my_parts = tile_runs(n_tiles_all, n_parts, run_tiles);
   const bool idle = part >= my_parts;                     // this tile has fewer runs than the launch has blocks per tile
   const int per_part = (n_tiles_all + my_parts - 1) / my_parts;
-  const int kt_begin = kt_first + part * per_part * BKV;
+  const int tile_begin = part * per_part;                 // this run's first tile of the walk
   const int n_tiles = idle ? 0 : max(0, min(per_part, n_tiles_all - part * per_part));
   kf_pdl_wait();                                          // Q, and the keys and values of this step's rows, come from the kernel before
 
@@ -299,7 +306,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       const int* tab = table + (size_t)req * table_stride;
       for (int i = 0; i < n_tiles; ++i) {
         const int s = i & 1;
-        const int kt = kt_begin + i * BKV;
+        const int kt = key_of_tile(tile_begin + i, kt_first, n_kept);
         int page = tab[kt / page_size];
         if (page < 0) page = 0;                            // a page already given back: every key of it is masked
         const int krow = ((page * 2 + 0) * hm.n_stored + hm.key) * page_size + (kt % page_size);
@@ -315,7 +322,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       const int* tab = table + (size_t)req * table_stride;
       for (int i = 0; i < n_tiles; ++i) {
         const int s = i & 1;
-        const int kt = kt_begin + i * BKV;
+        const int kt = key_of_tile(tile_begin + i, kt_first, n_kept);
         int page = tab[kt / page_size];
         if (page < 0) page = 0;
         const int vrow = ((page * 2 + 1) * hm.n_stored + hm.value) * page_size + (kt % page_size);
@@ -388,7 +395,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     for (int i = grp; i < n_tiles; i += 2) {
       ok = ok && mbar_wait(&s_full[grp], (i >> 1) & 1);
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const int kt = kt_begin + i * BKV;                   // first key of the tile
+      const int kt = key_of_tile(tile_begin + i, kt_first, n_kept);   // first key of the tile
       float sv[64];
       tmem_ld64(lane_addr + grp * S_COLS, sv);
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -425,8 +432,13 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         // key kt + c is seen by this row iff first <= c <= last: one bit per key, tested with constant masks
         const int last = prow - kt;                                        // >= 64: all of the tile
         const int first = window > 0 ? last - window + 1 : 0;              // <= 0: from the tile's first key
-        unsigned long long seen = last < 0 ? 0ull : (last >= 63 ? ~0ull : ((2ull << last) - 1ull));
+        const unsigned long long causal = last < 0 ? 0ull : (last >= 63 ? ~0ull : ((2ull << last) - 1ull));
+        unsigned long long seen = causal;
         if (first > 0) seen &= first >= 64 ? 0ull : ~((1ull << first) - 1ull);
+        if (keep_first > kt) {                                             // kept first tokens: seen wherever the window stands
+          const int nk = keep_first - kt;
+          seen |= causal & (nk >= 64 ? ~0ull : ((1ull << nk) - 1ull));
+        }
         const uint32_t seen_lo = (uint32_t)seen, seen_hi = (uint32_t)(seen >> 32);
 #pragma unroll
         for (int c = 0; c < 32; ++c) {
@@ -501,6 +513,14 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     s_max[half * BMQ + r] = l_sum;
     asm volatile("bar.sync 2, 256;" ::: "memory");
     l_sum = s_max[r] + s_max[BMQ + r];
+    // the sink (a key of score 0 without a value) adds 2^(0 - m) to the sum of the run that holds the walk's first tile
+    // (a run whose scores all lie far below zero, or that this row sees nothing of, leaves the sink alone: maximum 0, sum 1)
+    float m_rec = m_used;
+    bool sink_alone = false;
+    if (sink && part == 0 && n_tiles > 0) {
+      if (!(m_used > -100.f)) { m_rec = 0.f; l_sum = 1.f; sink_alone = true; }
+      else l_sum += ex2_fast(-m_used);
+    }
     if (idle) {
       // nothing to do and nothing to write
     } else if (my_parts > 1) {
@@ -508,13 +528,17 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       const bool run_ok = __all_sync(0xffffffffu, ok && n_tiles > 0 && *s_abort == 0);
       const bool have = run_ok && r < nrows && l_sum > 0.f;     // a row that saw no key in this run leaves m = -inf
       float* rec = partial + (((size_t)(row0 + (r < nrows ? r : 0)) * nh + h) * n_parts + part) * (D + 4);
-      if (half == 0 && r < nrows) { rec[D] = have ? m_used : -INFINITY; rec[D + 1] = have ? l_sum : 0.f; }
+      if (half == 0 && r < nrows) { rec[D] = have ? m_rec : -INFINITY; rec[D + 1] = have ? l_sum : 0.f; }
       if (run_ok) {
 #pragma unroll 1
         for (int c = 0; c < HC; c += 16) {
           float o[16];
           tmem_ld16(lane_addr + O_COL + half * HC + c, o);       // every lane of the warp takes part in the load
           if (have) {
+            if (sink_alone) {
+#pragma unroll
+              for (int e = 0; e < 16; ++e) o[e] = 0.f;
+            }
 #pragma unroll
             for (int e = 0; e < 16; e += 4)
               *reinterpret_cast<float4*>(rec + half * HC + c + e) = make_float4(o[e], o[e + 1], o[e + 2], o[e + 3]);
@@ -522,7 +546,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         }
       }
     } else if (ok && n_tiles > 0 && *s_abort == 0) {
-      const float inv = l_sum > 0.f ? 1.f / l_sum : 0.f;
+      const float inv = (l_sum > 0.f && !sink_alone) ? 1.f / l_sum : 0.f;
       __nv_bfloat16* orow = out + ((size_t)(row0 + r) * nh + h) * D + half * HC;
 #pragma unroll 1
       for (int c = 0; c < HC; c += 16) {
@@ -555,15 +579,15 @@ template <int D>
 __global__ void __launch_bounds__(128)
 attn_prefill_merge_kernel(const float* __restrict__ partial, const int* __restrict__ tile_row0,
                           const int* __restrict__ tile_nrows, const int* __restrict__ positions,
-                          const int* __restrict__ row_req, int window, int nh, int n_parts_max, int run_tiles,
-                          __nv_bfloat16* __restrict__ out) {
+                          const int* __restrict__ row_req, int window, int keep_first, int nh, int n_parts_max,
+                          int run_tiles, __nv_bfloat16* __restrict__ out) {
   kf_pdl_trigger();
   kf_pdl_wait();
   const int tile = blockIdx.x, r = blockIdx.y;
   if (r >= tile_nrows[tile]) return;
-  int kt_first;
-  const int n_parts = tile_runs(tile_key_tiles(tile_row0[tile], tile_nrows[tile], positions, row_req, window, &kt_first),
-                                n_parts_max, run_tiles);
+  int kt_first, n_kept;
+  const int n_parts = tile_runs(tile_key_tiles(tile_row0[tile], tile_nrows[tile], positions, row_req, window, keep_first,
+                                               &kt_first, &n_kept), n_parts_max, run_tiles);
   if (n_parts == 1) return;                                   // a tile with one run wrote its rows itself
   const int row = tile_row0[tile] + r;
   constexpr int REC = D + 4;
@@ -638,8 +662,8 @@ bool tensor_map(const void* base, long rows, long cols, int box_rows, CUtensorMa
 template <int D>
 int launch(const CUtensorMap& tq, const CUtensorMap& tkv, const int* tile_row0, const int* tile_nrows, int n_tiles,
            const int* positions, const int* row_req, const int* table, int table_stride, int page_size, int nh, int nkv,
-           float scale, float softcap, int window, int vsplit, void* out, int* error_flag, int n_parts, int run_tiles,
-           float* partial, cudaStream_t stream) {
+           float scale, float softcap, int window, int vsplit, int keep_first, int sink, void* out, int* error_flag,
+           int n_parts, int run_tiles, float* partial, cudaStream_t stream) {
   const size_t smem = (size_t)BMQ * D * 2 + 4 * (size_t)BKV * D * 2 + (size_t)BMQ * BKV * 2 + 1024 + 256 + 4 * BMQ * 4;
   static bool configured = false;
   if (!configured) {
@@ -650,12 +674,12 @@ int launch(const CUtensorMap& tq, const CUtensorMap& tkv, const int* tile_row0, 
     configured = true;
   }
   kf_launch(attn_prefill_tc_kernel<D>, dim3(n_tiles * n_parts * nh), dim3(THREADS), smem, stream, tq, tkv, tile_row0, tile_nrows,
-            positions, row_req, table, table_stride, page_size, nh, nkv, scale, softcap, window, vsplit, (__nv_bfloat16*)out,
-            error_flag, n_parts, run_tiles, partial);
+            positions, row_req, table, table_stride, page_size, nh, nkv, scale, softcap, window, vsplit, keep_first, sink,
+            (__nv_bfloat16*)out, error_flag, n_parts, run_tiles, partial);
   KF_CHECK_LAUNCH();
   if (n_parts > 1) {
     kf_launch(attn_prefill_merge_kernel<D>, dim3(n_tiles, BMQ), dim3(128), 0, stream, (const float*)partial, tile_row0,
-              tile_nrows, positions, row_req, window, nh, n_parts, run_tiles, (__nv_bfloat16*)out);
+              tile_nrows, positions, row_req, window, keep_first, nh, n_parts, run_tiles, (__nv_bfloat16*)out);
     KF_CHECK_LAUNCH();
   }
   return KF_OK;
@@ -713,15 +737,16 @@ KF_API int kf_attention_prefill_tc(const void* q, void* out, const void* pages, 
                                    const int* tile_nrows, int n_tiles, const int* positions, const int* row_req,
                                    const int* table, int table_stride, int page_size, int nh, int nkv, int d, float scale,
                                    float softcap, int window, int vsplit, int* error_flag, int n_parts, int run_tiles,
-                                   float* partial, cudaStream_t stream) {
+                                   float* partial, int keep_first, int sink, cudaStream_t stream) {
   if (n_tiles <= 0) return KF_OK;
+  if (window <= 0) keep_first = 0;
   if (nkv < 1 || nh % nkv != 0 || page_size % 64 != 0 || !kf_head_map_ok(nh, nkv, vsplit)) return KF_ERR_SIZE;
   const KfHeadMap hm = kf_head_map(0, 0, nh, nkv, vsplit);
   if (n_parts < 1 || n_parts > 8 || (n_parts > 1 && !partial) || run_tiles < 0) return KF_ERR_SIZE;
   CUtensorMap tq, tkv;
   if (!tensor_map(q, T, (long)hm.n_query * d, BMQ, &tq)) return KF_ERR_SETUP;
   if (!tensor_map(pages, n_pages * 2 * hm.n_stored * page_size, d, BKV, &tkv)) return KF_ERR_SETUP;
-#define KF_ARGS tq, tkv, tile_row0, tile_nrows, n_tiles, positions, row_req, table, table_stride, page_size, nh, nkv, scale, softcap, window, vsplit, out, error_flag, n_parts, run_tiles, partial, stream
+#define KF_ARGS tq, tkv, tile_row0, tile_nrows, n_tiles, positions, row_req, table, table_stride, page_size, nh, nkv, scale, softcap, window, vsplit, keep_first, sink, out, error_flag, n_parts, run_tiles, partial, stream
   switch (d) {
     case 64: return launch<64>(KF_ARGS);
     case 128: return launch<128>(KF_ARGS);

@@ -326,7 +326,9 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict_
     const float z = logits[(size_t)t * E + e];
     const float s = softmax ? expf(z - zmax) / zsum : 1.f / (1.f + expf(-z));
     score[e] = s;
-    const float c = s + (correction ? kf_load(correction, e) : 0.f);
+    // sigmoid scores without a correction and without groups rank as their logits do, and the logits do not run into
+    // one another where the sigmoid rounds to 1 (z > 17 in 32-bit)
+    const float c = (!softmax && !correction && G == 1) ? z : s + (correction ? kf_load(correction, e) : 0.f);
     choice[e] = c == c ? c : NEG;                      // a row of padding may hold anything
   }
   __syncwarp();

@@ -482,8 +482,9 @@ def paged_attention(q, out, ctx, cache, n_heads: int, n_kv_heads: int, head_dim:
               _f(scale), _f(softcap), int(window or 0), int(value_split))
     n_dec = getattr(ctx, "n_dec_rows", 0)
     fast = (use_fast_attention and q.dtype == torch.bfloat16 and pages.dtype == torch.bfloat16)
-    if (keep_first or sink) and (value_split or not extras_on_fast_kernels):
-        fast = False
+    if (keep_first or sink) and (value_split or not extras_on_fast_kernels or not decode_on_tensor_cores
+                               or n_heads // n_kv_heads > 16):
+        fast = False                                   # the generic kernel: every combination
     vs_splits = ctypes.c_int(0)
     own = decode_value_split_kernel if decode_value_split_kernel is not None else value_split >= 3
     if (fast and n_dec > 0 and value_split and softcap == 0.0 and own
@@ -503,7 +504,7 @@ def paged_attention(q, out, ctx, cache, n_heads: int, n_kv_heads: int, head_dim:
         rest, n_rest = ctx.pre_rows, ctx.n_pre_rows
     elif fast and n_dec > 0 and lib.kf_attention_decode_supported(head_dim):
         ht, splits = ctypes.c_int(0), ctypes.c_int(0)
-        max_keys = min(ctx.max_kv_len, window) if window else ctx.max_kv_len
+        max_keys = min(ctx.max_kv_len, window + keep_first) if window else ctx.max_kv_len
         group = n_heads // n_kv_heads
         if decode_on_tensor_cores and group <= 16:
             lib.kf_attention_decode_mma_plan(n_dec, n_heads, n_kv_heads, head_dim, int(max_keys), ctypes.byref(splits))
@@ -518,7 +519,7 @@ def paged_attention(q, out, ctx, cache, n_heads: int, n_kv_heads: int, head_dim:
             partial = _partial(q.device, T * n_heads * splits.value * (head_dim + 4)) if splits.value > 1 else None
             items = None if n_dec == T else ctx.dec_rows
             _check(lib.kf_attention_decode(_p(q), _p(out), _p(pages), _p(items), n_dec, *common, ht.value,
-                                           splits.value, _p(partial), _p(sc["counters"]), _stream()), "attention (decode)")
+                                           splits.value, _p(partial), _p(sc["counters"]), *extras, _stream()), "attention (decode)")
             if n_dec == T:
                 return
             rest, n_rest = ctx.pre_rows, ctx.n_pre_rows
@@ -530,7 +531,7 @@ def paged_attention(q, out, ctx, cache, n_heads: int, n_kv_heads: int, head_dim:
     if (prompt_tiles and prefill_on_tcgen05 and getattr(ctx, "n_wide", 0) > 0
             and lib.kf_attention_prefill_tc_supported(head_dim, cache.page_size, _p(q), _p(pages))):
         sc = _dev_scratch(q.device)
-        max_keys = min(ctx.max_kv_len, window + 128) if window else ctx.max_kv_len
+        max_keys = min(ctx.max_kv_len, window + 128 + -(-keep_first // 64) * 64) if window else ctx.max_kv_len
         run_tiles = ctypes.c_int(0)
         if prefill_plan_override is not None:
             parts, run_tiles = int(prefill_plan_override[0]), ctypes.c_int(int(prefill_plan_override[1]))
@@ -539,14 +540,14 @@ def paged_attention(q, out, ctx, cache, n_heads: int, n_kv_heads: int, head_dim:
         partial = _partial(q.device, T * n_heads * parts * (head_dim + 4)) if parts > 1 else None
         _check(lib.kf_attention_prefill_tc(_p(q), _p(out), _p(pages), ctypes.c_long(pages.shape[0]), T, _p(ctx.wide_row0),
                                            _p(ctx.wide_nrows), ctx.n_wide, *common, _p(sc["error"]), parts, run_tiles.value,
-                                           _p(partial), _stream()),
+                                           _p(partial), *extras, _stream()),
                "attention (prefill, tcgen05)")
         if parts > 1:
             add_launches(1)
         return
     if prompt_tiles and lib.kf_attention_prefill_supported(head_dim):
         _check(lib.kf_attention_prefill(_p(q), _p(out), _p(pages), _p(ctx.tile_row0), _p(ctx.tile_nrows), ctx.n_tiles,
-                                        *common, _stream()), "attention (prefill)")
+                                        *common, *extras, _stream()), "attention (prefill)")
         return
     if fast and use_fast_attention:
         note_fallback(f"attention: head size {head_dim} or page size {cache.page_size} has no tensor-core kernel")
@@ -555,7 +556,7 @@ def paged_attention(q, out, ctx, cache, n_heads: int, n_kv_heads: int, head_dim:
 
 
 # Whether the tensor-core attention kernels take `keep_first` and `sink`; False sends such launches to the generic kernel.
-extras_on_fast_kernels = False
+extras_on_fast_kernels = os.environ.get("KUNGFU_ATTENTION_EXTRAS_FAST", "1") != "0"
 
 # Decode rows of value-split attention: True, the kernel that owns all value heads of a tile of query heads; False, the
 # ordinary decode kernels (one block per pair of a key head and a value head); None, the former from three value heads on

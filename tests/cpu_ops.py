@@ -340,6 +340,8 @@ class CpuOps:
         z = torch.nan_to_num(logits.float())
         s = torch.softmax(z, dim=-1) if score == "softmax" else torch.sigmoid(z)
         choice = s + (correction.float()[None, :] if correction is not None else 0.0)
+        if score == "sigmoid" and correction is None and groups == 1:
+            choice = z                              # the same ranking, without the ties of a sigmoid that rounds to 1
         if groups > 1:
             per = E // groups
             g = choice.view(T, groups, per)

@@ -14,7 +14,8 @@ F = torch.float64
 # What a 16-bit serving path may round: the inputs of matrix products, queries, keys and values as the attention reads
 # them, the attention's weights, the feed-forwards' inner rows.  `ROUND` is applied at those places; the identity by
 # default.  `rounded_to_bfloat16()` switches it for a block of code: a yardstick of what 8-bit mantissas alone do.
-ROUND = lambda t: t
+_EXACT = lambda t: t
+ROUND = _EXACT
 
 
 class rounded_to_bfloat16:
@@ -231,15 +232,36 @@ def latent_attention(h, w, p: str, m: dict, eps: float, positions):
     k_rot = down[:, rank:].view(T, 1, r)
     k_flat = linear(c, w[p + "uk"]).view(T, H, d)
     v = linear(c, w[p + "uv"]).view(T, H, dv)
-    rot = dict(m["rot"])
-    f, mag = ramp_scaled_frequencies(rot)
-    q_rot = rotate(q[..., d:], positions, f, r, True, mag)
-    k_rot = rotate(k_rot, positions, f, r, True, mag)
-    qq = torch.cat([q[..., :d], q_rot], dim=-1)
-    kk = torch.cat([k_flat, k_rot.expand(T, H, r)], dim=-1)
-    o = attend(qq, kk, v, float(m["scale"]), visible(T, None, 0), sink=False)
+    if m.get("rot"):
+        f, mag = ramp_scaled_frequencies(dict(m["rot"]))
+        q_rot = rotate(q[..., d:], positions, f, r, True, mag)
+        k_rot = rotate(k_rot, positions, f, r, True, mag)
+    else:
+        q_rot = q[..., d:]
+    if ROUND is not _EXACT:                                  # a 16-bit path caches c alone and rounds in the latent space
+        o = latent_space_attention(q[..., :d], q_rot, c, k_rot, w, p, m)
+    else:
+        qq = torch.cat([q[..., :d], q_rot], dim=-1)
+        kk = torch.cat([k_flat, k_rot.expand(T, H, r)], dim=-1)
+        o = attend(qq, kk, v, float(m["scale"]), visible(T, None, 0), sink=False)
     o = head_gated(o, h, w[p + "g"])
     return linear(o.reshape(T, -1), w[p + "o"])
+
+
+def latent_space_attention(q_flat, q_rot, c, k_rot, w, p: str, m: dict):
+    """The same attention with every query taken into the latent space, q_h . (W_uk,h c) = (W_uk,h^T q_h) . c, and the
+    values' map applied after the weighted sum, sum_j a_j W_uv,h c_j = W_uv,h sum_j a_j c_j: equal in exact arithmetic; a
+    16-bit path that caches c alone rounds here (the queries in the latent space, c, the weighted sums of c)."""
+    T, H, d = q_flat.shape
+    rank, dv, r = c.shape[-1], int(m["vdim"]), q_rot.shape[-1]
+    uk = w[p + "uk"].to(F).view(H, d, rank)
+    uv = w[p + "uv"].to(F).view(H, dv, rank)
+    qa = torch.einsum("thd,hdr->thr", ROUND(q_flat), uk)
+    qq = torch.cat([qa, q_rot], dim=-1)
+    kk = torch.cat([c, k_rot[:, 0]], dim=-1)[:, None, :]
+    vv = torch.cat([c, torch.zeros(T, r, dtype=F)], dim=-1)[:, None, :]
+    o = attend(qq, kk, vv, float(m["scale"]), visible(T, None, 0), sink=False)
+    return ROUND(torch.einsum("thr,hvr->thv", ROUND(o[..., :rank]), uv))
 
 
 # ---- feed-forward --------------------------------------------------------------------------------------------------

@@ -249,6 +249,22 @@ def test_plain_latent_attention_shares_one_rotated_key_part():
     assert not torch.allclose(base, pn.latent_attention(h, t2, "l0.mix.", m, 1e-6, torch.arange(6)), atol=1e-6)
 
 
+def test_plain_latent_space_form_is_the_same_attention():
+    """Queries taken into the latent space and the values' map applied after the weighted sum: the same numbers."""
+    cfg = nk.config(32, 50, [nk.layer("latent_attention", nk.latent(3, 6, 4, 5, 9, 7, 0.5, 100.0, (2.0, 8, 2.0, 1.0)))])
+    t = nk.draw_tensors(cfg, 6)
+    h = torch.randn(11, 32, generator=torch.Generator().manual_seed(2), dtype=D64)
+    m = cfg["layers"][0]["mixer"]
+    plain = pn.latent_attention(h, t, "l0.mix.", m, 1e-6, torch.arange(11))
+    saved = pn.ROUND
+    pn.ROUND = lambda x: x * 1.0                               # not the marker of exact arithmetic, and yet exact
+    try:
+        other = pn.latent_attention(h, t, "l0.mix.", m, 1e-6, torch.arange(11))
+    finally:
+        pn.ROUND = saved
+    assert torch.allclose(plain, other, atol=1e-12)
+
+
 # ---- the engine's host logic ------------------------------------------------------------------------------------------
 
 @pytest.mark.parametrize("name", ["A", "B", "C", "D"])
