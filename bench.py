@@ -8,6 +8,7 @@
     python bench.py --compare bolonex
     python bench.py --compare petanex
     python bench.py --compare pimodra
+    python bench.py --compare nukelix
                     (Bolonex beside Gemma 2, or Petanex beside Bolonex, at equal layer sizes: prefill and decode throughput
                     and, per operation, the time of one step against the time its bytes, or its multiply-adds, take at the
                     measured rates; one JSON line)
@@ -730,6 +731,75 @@ def compare_pimodra(args) -> dict:
                                                                       ("gemma2", gemma_twin_config(z), gemma_op_bytes)))
 
 
+# ---- Nukelix beside Petanex at equal layer sizes (--compare nukelix) ---------------------------------------------------
+# Eight layers in both.  Nukelix: windowed attention with kept first tokens, two layers of attention beside a matrix
+# memory, latent attention with a shared rotated key part, twice; every feed-forward a mixture whose chosen experts and
+# shared expert together have the dense width.  Petanex (the closest existing model: attention over a latent, a 32-bit
+# recurrence with a d x dv state per head, mixtures with a shared expert) as in --compare petanex.  Same width, heads,
+# head size, state size per head, experts and vocabulary.
+NUKELIX_SIZES = {
+    "w2048": dict(PETANEX_SIZES["w2048"], q_rank=512, kv_rank=192, rot_dim=64, window=1024, keep_first=64),
+    "w4096": dict(PETANEX_SIZES["w4096"], q_rank=1024, kv_rank=192, rot_dim=64, window=1024, keep_first=64),
+}
+
+
+def nukelix_config(z: dict) -> dict:
+    d = z["dim"]
+    att = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": d, "vdim": d, "scale": d ** -0.5, "v_mix": True,
+           "mask": {"size": z["window"], "keep_first": z["keep_first"]},
+           "rot": {"base": 500000.0, "dims": d // 2, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}
+    left = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": d, "vdim": d, "scale": d ** -0.5,
+            "rot": {"base": 1000000.0, "dims": d}}
+    par = {"left": left, "left_scale": 0.8, "right_scale": 0.9,
+           "right": {"heads": z["d_heads"], "dim": z["d_dim"], "vdim": z["d_vdim"], "gate_cap": 15.0}}
+    lat = {"heads": z["lat_heads"], "dim": d, "rot_dim": z["rot_dim"], "vdim": d, "kv_rank": z["kv_rank"], "q_rank": z["q_rank"],
+           "scale": (d + z["rot_dim"]) ** -0.5,
+           "rot": {"base": 10000.0, "dims": z["rot_dim"], "scaling": {"factor": 4.0, "original": 2048, "fast": 32.0, "slow": 1.0}}}
+    eff = z["ff"] // (z["top"] + 1) // 64 * 64
+    moe = {"kind": "moe", "expert": {"ff": eff}, "shared": {"ff": eff}, "router": {"experts": z["experts"], "top": z["top"]}}
+    kinds = ["attention", "parallel", "parallel", "latent_attention"]
+    layers = [{"type": kinds[i % 4], "mixer": (att, par, par, lat)[i % 4], "mlp": moe} for i in range(COMPARE_LAYERS)]
+    return {"architecture": "Nukelix", "width": z["width"], "vocab": COMPARE_VOCAB, "norm": {"eps": 1e-6},
+            "logit_softcap": 30.0, "layers": layers}
+
+
+def nukelix_op_bytes(z: dict, T: int, n_reqs: int, keys: int) -> dict:
+    """Bytes (and, for the grouped products, floating-point operations) each operation of one Nukelix step must move,
+    summed over the layers that use it."""
+    W, H, G, d, L = z["width"], z["heads"], z["kv_heads"], z["dim"], COMPARE_LAYERS
+    n_att, n_par, n_lat = L // 4, L // 2, L // 4
+    cq = (H + 2 * G) * d
+    mh, md, mv = z["d_heads"], z["d_dim"], z["d_vdim"]
+    lh, rank, rd = z["lat_heads"], z["kv_rank"], z["rot_dim"]
+    D = 256 if rank + rd > 128 else 128
+    seen = min(keys, z["window"] + z["keep_first"])
+    eff = z["ff"] // (z["top"] + 1) // 64 * 64
+    P = T * z["top"]
+    used = min(z["experts"], P)
+    return {
+        "rownorm_rope_append": (n_att + n_par) * T * (4 * cq + 2 * cq + 4 * d),
+        "paged_attention": n_att * (n_reqs * seen * 2 * G * d * 2 + T * H * d * 4) + n_par * (n_reqs * keys * 2 * G * d * 2 + T * H * d * 4)
+                           + n_lat * (n_reqs * keys * 2 * D * 2 + T * lh * D * 4),
+        "head_gate": (n_att + n_par + n_lat) * T * H * d * 4,
+        "mlstm": n_par * (T * mh * (2 * md + 2 * mv) * 4 + 2 * n_reqs * mh * md * mv * 4),
+        "head_norm_gate": n_par * T * mh * mv * 10,
+        "weighted_sum2": n_par * T * W * 12,
+        "latent_rope_append": n_lat * T * ((rank + rd) * 4 + 4 * D + lh * rd * 8),
+        "cols_rmsnorm": n_lat * T * z["q_rank"] * 6,
+        "head_linear": (n_lat * T * lh * (4 * (d + rd) + 2 * D + 2 * D + 2 * d), n_lat * 2 * T * lh * (D * (d + rd) + d * D)),
+        "add_rmsnorm": 2 * L * T * W * 14,
+        "moe_route": L * T * (z["experts"] * 4 + z["top"] * 8),
+        "moe_plan": L * P * 12,
+        "moe_linear": (L * (used * 3 * eff * W * 2 + P * (2 * W + 4 * eff + 4 * W)), L * 6 * P * eff * W),
+        "moe_combine": L * T * W * (4 * z["top"] + 8),
+    }
+
+
+def compare_nukelix(args) -> dict:
+    return compare_models(args, "nukelix", NUKELIX_SIZES, lambda z: (("nukelix", nukelix_config(z), nukelix_op_bytes),
+                                                                      ("petanex", petanex_config(z), petanex_op_bytes)))
+
+
 def micro_attention() -> int:
     """Decode attention alone: eight launches over distinct pages replayed from a CUDA graph, per batch size; one JSON
     line each with microseconds per launch and bytes of keys and values over that time."""
@@ -1143,14 +1213,15 @@ def main() -> int:
     ap.add_argument("--only-headline", action="store_true", help="skip the other batch sizes, the mixed steps, 32-bit and the other model sizes")
     ap.add_argument("--micro", choices=["attention", "prompt-attention", "gemm", "products", "qkv-rope", "reference"],
                     help="time kernels alone instead of the model step")
-    ap.add_argument("--compare", choices=["bolonex", "petanex", "pimodra"],
+    ap.add_argument("--compare", choices=["bolonex", "petanex", "pimodra", "nukelix"],
                     help="another workload: Bolonex beside Gemma 2, Petanex beside Bolonex, or Pimodra beside Gemma 2, at equal "
                          "layer sizes (prefill, decode, per-operation rooflines)")
     args = ap.parse_args()
     if args.compare:
         args.warmup = max(args.warmup, 3)
         args.reps = max(args.reps, 1)
-        print(json.dumps({"bolonex": compare_bolonex, "petanex": compare_petanex, "pimodra": compare_pimodra}[args.compare](args)))
+        print(json.dumps({"bolonex": compare_bolonex, "petanex": compare_petanex, "pimodra": compare_pimodra,
+                          "nukelix": compare_nukelix}[args.compare](args)))
         return 0
     if args.micro:
         return {"attention": micro_attention, "prompt-attention": micro_prompt_attention, "gemm": micro_gemm,

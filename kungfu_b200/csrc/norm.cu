@@ -75,7 +75,7 @@ __global__ void __launch_bounds__(MAXT) add_rmsnorm_reg_kernel(const float* a, c
   for (int k = 0; k < NPT; ++k) {
     const int i = threadIdx.x + k * blockDim.x;
     g1[k] = i < H ? kf_load(w1, i) + (plus1 ? 1.f : 0.f) : 0.f;
-    g2[k] = (i < H && out2 != nullptr) ? kf_load(w2, i) + (plus2 ? 1.f : 0.f) : 0.f;
+    g2[k] = (i < H && out2 != nullptr) ? (plus2 == 2 ? 1.f : kf_load(w2, i) + (plus2 ? 1.f : 0.f)) : 0.f;
   }
   kf_pdl_wait();
   a = kf_produced(a), x = kf_produced(x);
@@ -105,7 +105,7 @@ __global__ void __launch_bounds__(MAXT) add_rmsnorm_reg_kernel(const float* a, c
   }
   if (out2 == nullptr) return;
   ss2 = kf_block_sum(ss2, red);
-  const float inv2 = 1.f / sqrtf(ss2 / (float)H + eps2);
+  const float inv2 = plus2 == 2 ? 1.f : 1.f / sqrtf(ss2 / (float)H + eps2);
   TO* o = out2 + (size_t)r * H;
 #pragma unroll
   for (int k = 0; k < NPT; ++k) {
@@ -118,6 +118,7 @@ __global__ void __launch_bounds__(MAXT) add_rmsnorm_reg_kernel(const float* a, c
 // Needs H % 4 == 0 and H <= 128 * NV4.
 template <typename TW>
 __device__ __forceinline__ float4 kf_gain4(const TW* w, int i, int plus_one) {
+  if (plus_one == 2) return make_float4(1.f, 1.f, 1.f, 1.f);        // no norm at all: the rows pass as they are
   const float p = plus_one ? 1.f : 0.f;
   return make_float4(kf_load(w, i) + p, kf_load(w, i + 1) + p, kf_load(w, i + 2) + p, kf_load(w, i + 3) + p);
 }
@@ -162,7 +163,7 @@ add_rmsnorm_warp_kernel(const float* __restrict__ a, const TW1* __restrict__ w1,
   }
   if (out2 == nullptr) return;
   ss2 = kf_warp_sum(ss2);
-  const float inv2 = 1.f / sqrtf(ss2 / (float)H + eps2);
+  const float inv2 = plus2 == 2 ? 1.f : 1.f / sqrtf(ss2 / (float)H + eps2);
   TO* o = out2 + (size_t)r * H;
 #pragma unroll
   for (int k = 0; k < NV4; ++k) {
@@ -232,10 +233,10 @@ __global__ void add_rmsnorm_kernel(const float* __restrict__ a, const TW1* __res
   }
   if (out2 == nullptr) return;
   ss2 = kf_block_sum(ss2, red);
-  const float inv2 = 1.f / sqrtf(ss2 / (float)H + eps2);
+  const float inv2 = plus2 == 2 ? 1.f : 1.f / sqrtf(ss2 / (float)H + eps2);
   TO* o = out2 + (size_t)r * H;
   for (int i = threadIdx.x; i < H; i += blockDim.x) {     // each thread re-reads only what it wrote
-    const float g = kf_load(w2, i) + (plus2 ? 1.f : 0.f);
+    const float g = plus2 == 2 ? 1.f : kf_load(w2, i) + (plus2 ? 1.f : 0.f);
     kf_store(o, i, xr[i] * inv2 * g);
   }
 }
@@ -289,7 +290,7 @@ add_rmsnorm_split_kernel(const float* __restrict__ a, const TW1* __restrict__ w1
   if (lane == 0) red[1][warp] = ss2;
   __syncthreads();
   ss2 = red[1][warp & ~1] + red[1][warp | 1];
-  const float inv2 = 1.f / sqrtf(ss2 / (float)H + eps2);
+  const float inv2 = plus2 == 2 ? 1.f : 1.f / sqrtf(ss2 / (float)H + eps2);
   TO* o = out2 + (size_t)(valid ? r : 0) * H;
 #pragma unroll
   for (int k = 0; k < NV; ++k) {

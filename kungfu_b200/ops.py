@@ -271,9 +271,17 @@ def rmsnorm(x, weight, eps: float, plus_one: bool, out, rows=None) -> None:
 
 @_dispatch("add_rmsnorm")
 def add_rmsnorm(branch, weight, eps: float, plus_one: bool, residual, *, next_weight=None, next_eps: float = 0.0,
-                next_plus_one: bool = False, next_out=None) -> None:
-    """residual += rmsnorm(branch) * g; if next_out is given, next_out = rmsnorm(residual) * g_next."""
+                next_plus_one: bool = False, next_out=None, copy_out=None) -> None:
+    """residual += rmsnorm(branch) * g; if next_out is given, next_out = rmsnorm(residual) * g_next; if copy_out is given
+    (instead), copy_out = the new residual rows in copy_out's element type (for a sublayer that reads the stream itself)."""
     T, H = residual.shape
+    if copy_out is not None:
+        if next_out is not None:
+            raise KernelError("add_rmsnorm: either the next norm or a plain copy, not both")
+        _check(library().kf_add_rmsnorm(_p(branch), _p(weight), _dt(weight), _f(eps), int(plus_one), _p(residual),
+                                        _p(weight), _dt(weight), _f(0.0), 2, _p(copy_out), _dt(copy_out), T, H, _stream()),
+               "add_rmsnorm")
+        return
     _check(library().kf_add_rmsnorm(_p(branch), _p(weight), _dt(weight), _f(eps), int(plus_one), _p(residual),
                                     _p(next_weight), _dt(next_weight) if next_weight is not None else F32, _f(next_eps),
                                     int(next_plus_one), _p(next_out), _dt(next_out) if next_out is not None else F32,

@@ -36,6 +36,10 @@ class RmsNorm(Norm):
             ops.add_rmsnorm(branch, self.weight, self.eps, self.plus_one, residual,
                             next_weight=then.weight, next_eps=then.eps, next_plus_one=then.plus_one, next_out=out)
             return out
+        if isinstance(then, NoNorm) and out_dtype != residual.dtype:
+            out = ctx.buf("norm_out", (residual.shape[0], self.width), out_dtype)       # the sum and the copy in one kernel
+            ops.add_rmsnorm(branch, self.weight, self.eps, self.plus_one, residual, copy_out=out)
+            return out
         ops.add_rmsnorm(branch, self.weight, self.eps, self.plus_one, residual)
         return then.forward(residual, ctx, out_dtype)
 

@@ -33,9 +33,11 @@ class CpuOps:
         out.copy_((xs * inv * g).to(out.dtype))
 
     def add_rmsnorm(self, branch, weight, eps, plus_one, residual, *, next_weight=None, next_eps=0.0,
-                    next_plus_one=False, next_out=None):
+                    next_plus_one=False, next_out=None, copy_out=None):
         inv = torch.rsqrt(branch.pow(2).mean(-1, keepdim=True) + eps)
         residual.add_(branch * inv * (weight.float() + (1.0 if plus_one else 0.0)))
+        if copy_out is not None:
+            copy_out.copy_(residual.to(copy_out.dtype))
         if next_out is not None:
             self.rmsnorm(residual, next_weight, next_eps, next_plus_one, next_out)
 
