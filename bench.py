@@ -3,7 +3,7 @@
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
                     [--size 2b|9b|27b] [--layers L] [--batch B] [--context C] [--only-headline]
-    python bench.py --micro attention|prompt-attention|gemm|products|reference
+    python bench.py --micro attention|prompt-attention|gemm|products|reference|memory
                     (kernels alone, JSON lines; for the summaries in profiles/)
     python bench.py --compare bolonex
     python bench.py --compare petanex
@@ -917,6 +917,47 @@ def micro_prompt_attention() -> int:
     return 0
 
 
+def micro_memory() -> int:
+    """The matrix memory's walk alone (gates and walk, `ops.mlstm`) over one prompt of 2,048 rows and over 8 single rows, at
+    16 heads of 128 x 128, timed with CUDA events; one JSON line per case with microseconds and the bytes it must move."""
+    import types
+    import torch
+    from kungfu_b200 import api, ops
+    device = api.require_cuda("cuda:0")
+    ops.library()
+    H, d, dv = 16, 128, 128
+    width = 2 * H * d + 2 * H * dv + 2 * H
+    for rows, reqs in ((2048, 1), (8, 8)):
+        per = rows // reqs
+        proj = torch.randn(rows, width, device=device)
+        bufs = {}
+        ctx = types.SimpleNamespace(
+            n_reqs=reqs, req_row_start=torch.arange(0, rows, per, dtype=torch.int32, device=device),
+            req_n_rows=torch.full((reqs,), per, dtype=torch.int32, device=device),
+            req_state_slot=torch.arange(reqs, dtype=torch.int32, device=device),
+            buf=lambda tag, shape, dt: bufs.setdefault(tag, torch.empty(shape, dtype=dt, device=device)))
+        memory = torch.zeros(reqs, H, d, dv, device=device)
+        norm_state = torch.zeros(reqs, H, d + 4, device=device)
+        bias = torch.zeros(H, device=device, dtype=torch.bfloat16)
+        out = torch.empty(rows, H * dv, device=device)
+        run = lambda: ops.mlstm(proj, 0, H * d, 2 * H * d, 2 * H * d + 2 * H * dv, 2 * H * d + 2 * H * dv + H, bias, bias + 4.0, 15.0,
+                                memory, norm_state, out, H, d, dv, ctx)
+        for _ in range(3):
+            run()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(5):
+            run()
+        e1.record()
+        torch.cuda.synchronize()
+        nbytes = rows * H * (2 * d + 2 * dv) * 4 + 2 * reqs * H * d * dv * 4
+        print(json.dumps({"micro": "matrix memory", "rows": rows, "requests": reqs, "heads": H, "dim": d, "vdim": dv,
+                          "us": round(e0.elapsed_time(e1) / 5 * 1e3, 1), "bytes": nbytes}), flush=True)
+    ops.raise_on_device_error()
+    return 0
+
+
 def micro_gemm() -> int:
     """One square bfloat16 product (8192 cubed) on the tensor-core kernel, timed with CUDA events; one JSON line."""
     import torch
@@ -1211,7 +1252,7 @@ def main() -> int:
     ap.add_argument("--context", type=int, default=8192)
     ap.add_argument("--prefill-tokens", type=int, default=2048)
     ap.add_argument("--only-headline", action="store_true", help="skip the other batch sizes, the mixed steps, 32-bit and the other model sizes")
-    ap.add_argument("--micro", choices=["attention", "prompt-attention", "gemm", "products", "qkv-rope", "reference"],
+    ap.add_argument("--micro", choices=["attention", "prompt-attention", "gemm", "products", "qkv-rope", "reference", "memory"],
                     help="time kernels alone instead of the model step")
     ap.add_argument("--compare", choices=["bolonex", "petanex", "pimodra", "nukelix"],
                     help="another workload: Bolonex beside Gemma 2, Petanex beside Bolonex, or Pimodra beside Gemma 2, at equal "
@@ -1226,7 +1267,7 @@ def main() -> int:
     if args.micro:
         return {"attention": micro_attention, "prompt-attention": micro_prompt_attention, "gemm": micro_gemm,
                 "products": lambda: micro_products(args.size), "qkv-rope": lambda: micro_qkv_rope(args.size),
-                "reference": micro_reference}[args.micro]()
+                "reference": micro_reference, "memory": micro_memory}[args.micro]()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable": "nickheyer/kungfu is a Rust workspace (no setup.py or "
                           "pyproject.toml; pip: 'not installable') and this image has no cargo/rustc and no network, so it cannot be built "
