@@ -749,8 +749,8 @@ def nukelix_config(z: dict) -> dict:
            "mask": {"size": z["window"], "keep_first": z["keep_first"]},
            "rot": {"base": 500000.0, "dims": d // 2, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}
     left = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": d, "vdim": d, "scale": d ** -0.5,
-            "rot": {"base": 1000000.0, "dims": d}}
-    par = {"left": left, "left_scale": 0.8, "right_scale": 0.9,
+            "rot": {"base": 10000.0, "dims": d}}
+    par = {"left": left, "left_scale": 0.7, "right_scale": 1.2,
            "right": {"heads": z["d_heads"], "dim": z["d_dim"], "vdim": z["d_vdim"], "gate_cap": 15.0}}
     lat = {"heads": z["lat_heads"], "dim": d, "rot_dim": z["rot_dim"], "vdim": d, "kv_rank": z["kv_rank"], "q_rank": z["q_rank"],
            "scale": (d + z["rot_dim"]) ** -0.5,
@@ -760,7 +760,7 @@ def nukelix_config(z: dict) -> dict:
     kinds = ["attention", "parallel", "parallel", "latent_attention"]
     layers = [{"type": kinds[i % 4], "mixer": (att, par, par, lat)[i % 4], "mlp": moe} for i in range(COMPARE_LAYERS)]
     return {"architecture": "Nukelix", "width": z["width"], "vocab": COMPARE_VOCAB, "norm": {"eps": 1e-6},
-            "logit_softcap": 30.0, "layers": layers}
+            "logit_softcap": 50.0, "layers": layers}
 
 
 def nukelix_op_bytes(z: dict, T: int, n_reqs: int, keys: int) -> dict:

@@ -218,8 +218,8 @@ class NukelixConfig:
                 if not m.right.gate_cap > 0:
                     raise ConfigError(f"{at}: right: gate_cap must be positive, found {m.right.gate_cap}")
             else:
-                if m.kv_rank + m.rot_dim > 256:
-                    raise ConfigError(f"{at}: kv_rank + rot_dim above 256 is not supported, found {m.kv_rank + m.rot_dim}")
+                if m.kv_rank + m.rot_dim > 512:
+                    raise ConfigError(f"{at}: kv_rank + rot_dim above 512 is not supported, found {m.kv_rank + m.rot_dim}")
                 if m.rot_dim % 2 or (m.rot is not None and m.rot.dims != m.rot_dim):
                     raise ConfigError(f"{at}: rot_dim {m.rot_dim} must be even and equal to rot.dims")
                 if (m.rot is None) != (m.rot_dim == 0):
@@ -280,12 +280,13 @@ class NukelixConfig:
     def state_summary(self, element_size: int = 2) -> list:
         """Per layer, what it keeps per request: bytes per token of its pages, the window that bounds them, fixed bytes."""
         from ..ops import attention_head_size
+        from ..parts.latent import latent_head_size
         out = []
         for i, l in enumerate(self.layers):
             m = l.mixer
             if l.type == LATENT:
                 out.append({"layer": i, "kind": "latent_pages", "window": None, "fixed_bytes": 0,
-                            "bytes_per_token": 2 * attention_head_size(m.kv_rank + m.rot_dim) * element_size})
+                            "bytes_per_token": 2 * latent_head_size(m.kv_rank + m.rot_dim) * element_size})
                 continue
             a = m if l.type == ATTENTION else m.left
             fixed = 0

@@ -1,4 +1,4 @@
-// Paged attention for any head size up to 256, any number of heads and groups, any page size:
+// Paged attention for any head size up to 512 (an instance for heads up to 256 and one beyond), any number of heads and groups, any page size:
 // one warp per (token row, query head), exact 32-bit arithmetic (expf, tanhf, no fast-math).
 //
 // For the row at position p of request r the warp walks keys lo..p in ascending chunks of 32,
@@ -14,10 +14,10 @@
 // the bfloat16 path for head sizes the tensor-core kernels do not take.
 #include "common.cuh"
 
-constexpr int MAX_D = 256;
+constexpr int MAX_D_ALL = 512;
 constexpr int WARPS = 4;
 
-template <typename TQ, typename TKV>
+template <typename TQ, typename TKV, int MAX_D>
 __global__ void __launch_bounds__(WARPS * 32)
 attention_generic_kernel(const TQ* __restrict__ q, TQ* __restrict__ out, const TKV* __restrict__ pages,
                          const int* __restrict__ items, const int* __restrict__ positions,
@@ -103,17 +103,19 @@ KF_API int kf_attention_generic(const void* q, void* out, int q_dtype, const voi
                                 int page_size, int nh, int nkv, int d, float scale, float softcap, int window,
                                 int vsplit, int keep_first, int sink, int T, cudaStream_t stream) {
   if (T <= 0) return KF_OK;
-  if (d < 1 || d > MAX_D || nkv < 1 || nh % nkv != 0 || page_size < 1 || !kf_head_map_ok(nh, nkv, vsplit)) return KF_ERR_SIZE;
+  if (d < 1 || d > MAX_D_ALL || nkv < 1 || nh % nkv != 0 || page_size < 1 || !kf_head_map_ok(nh, nkv, vsplit)) return KF_ERR_SIZE;
   const long n_work = (long)T * nh;
   const int blocks = (int)((n_work + WARPS - 1) / WARPS);
-#define KF_GO(TQ, TKV)                                                                                     \
-  kf_launch(attention_generic_kernel<TQ, TKV>, dim3(blocks), dim3(WARPS * 32), 0, stream,                                     \
+#define KF_GO1(TQ, TKV, MAXD)                                                                              \
+  kf_launch(attention_generic_kernel<TQ, TKV, MAXD>, dim3(blocks), dim3(WARPS * 32), 0, stream,                               \
       (const TQ*)q, (TQ*)out, (const TKV*)pages, items, positions, row_req, block_table, table_stride, page_size, \
       nh, nkv, d, scale, softcap, window, vsplit, window > 0 ? keep_first : 0, sink, T)
+#define KF_GO(TQ, TKV) do { if (d <= 256) KF_GO1(TQ, TKV, 256); else KF_GO1(TQ, TKV, 512); } while (0)
   if (q_dtype == KF_F32 && kv_dtype == KF_F32) KF_GO(float, float);
   else if (q_dtype == KF_BF16 && kv_dtype == KF_BF16) KF_GO(__nv_bfloat16, __nv_bfloat16);
   else return KF_ERR_DTYPE;
 #undef KF_GO
+#undef KF_GO1
   KF_CHECK_LAUNCH();
   return KF_OK;
 }

@@ -19,6 +19,7 @@ _STATUS = {1: "unsupported combination of element types", 2: "unsupported size",
            4: "alignment rule broken", 5: "one-time set-up failed"}
 
 MAX_HEAD_DIM = 256
+MAX_GENERIC_HEAD_DIM = 512      # the generic attention kernel alone takes heads above MAX_HEAD_DIM, up to this
 
 
 class KernelError(RuntimeError):
@@ -231,10 +232,11 @@ def _dispatch(name):
 
 # ---- size rules ---------------------------------------------------------------------------------------
 
-def check_attention_sizes(n_heads: int, n_kv_heads: int, head_dim: int) -> None:
-    """Head sizes the attention kernels take: 2..256, even.  Anything else is refused here, at build time."""
-    if head_dim < 2 or head_dim > MAX_HEAD_DIM or head_dim % 2:
-        raise KernelError(f"head_dim {head_dim} is not supported: the attention kernels take even sizes up to {MAX_HEAD_DIM}")
+def check_attention_sizes(n_heads: int, n_kv_heads: int, head_dim: int, largest: int = MAX_HEAD_DIM) -> None:
+    """Head sizes the attention kernels take: 2..256, even.  Anything else is refused here, at build time.  (`largest` up to
+    MAX_GENERIC_HEAD_DIM for a mixer that accepts the generic kernel alone above 256: a latent's stored head.)"""
+    if head_dim < 2 or head_dim > min(largest, MAX_GENERIC_HEAD_DIM) or head_dim % 2:
+        raise KernelError(f"head_dim {head_dim} is not supported: the attention kernels take even sizes up to {largest}")
     if n_kv_heads < 1 or n_heads % n_kv_heads:
         raise KernelError(f"n_heads {n_heads} must be a multiple of n_kv_heads {n_kv_heads}")
 

@@ -28,7 +28,7 @@ import torch
 from .. import ops
 from .base import Mixer, PagedKV, PositionEncoding, pad_rows, register_mixer
 
-_KERNEL_HEAD_SIZES = (16, 32, 64, 128, 256)
+_KERNEL_HEAD_SIZES = (16, 32, 64, 128, 256, 384, 512)          # above 256 the generic attention kernel alone
 
 
 def latent_head_size(rank: int) -> int:
@@ -103,7 +103,7 @@ class LatentAttention(Mixer):
         self.c_col = self.q_rank if self.q_latent else self.q_width
         self.g_col = self.c_col + r + rd
         self.proj_width = max(self.g_col + (H if self.gated else 0), self.w_in.shape[0])
-        ops.check_attention_sizes(H, 1, D)
+        ops.check_attention_sizes(H, 1, D, largest=_KERNEL_HEAD_SIZES[-1])
 
     def state_need(self):
         return PagedKV(1, self.head_dim, self.window)

@@ -109,7 +109,7 @@ NK_E = config(512, 3000, [
     layer("parallel", parallel(left(4, 4, 128, 64, 0.07, rot(64, 5000.0)), 4, 64, 64, 10.0, 0.8, 1.2), moe(8, 2, 256)),
     layer("latent_attention", latent(8, 32, 32, 64, 96, 64, 0.12, 1000.0, (2.0, 64, 8.0, 2.0)), moe(16, 1, 64, shared=128)),
     layer("attention", attention(4, 2, 32, 64, 0.15, window=40, keep_first=70, rotation=rot(32, 1000.0), v_mix=True), moe(4, 3, 192)),
-    layer("parallel", parallel(left(8, 2, 64, 32, 0.1, rot(32, 10000.0)), 2, 32, 128, 12.0, 1.1, 0.6))], eps=1e-6, softcap=30.0)
+    layer("parallel", parallel(left(8, 2, 64, 32, 0.1, rot(32, 10000.0)), 2, 32, 128, 11.0, 1.1, 0.6))], eps=1e-6, softcap=25.0)
 
 CASES = {"A": (NK_A, [5, 17, 23, 40, 11, 30], 4), "B": (NK_B, [1, 31, 40, 70, 9, 50], 8), "C": (NK_C, [3, 50, 64, 29, 77, 2], 16),
          "D": (NK_D, [4, 19, 1, 33, 8, 12], 4)}

@@ -171,12 +171,14 @@ ONE_LAYER = {
     "mixed_values": nk.config(64, 200, [nk.layer("attention", nk.attention(2, 2, 8, 8, 0.4, window=30, keep_first=2, v_mix=True)),
                                         nk.layer("attention", nk.attention(4, 2, 16, 8, 0.3, window=9, keep_first=0, v_mix=True))]),
     # tensor-core head sizes, a window longer than a page
-    "windowed_wide": nk.config(128, 200, [nk.layer("attention", nk.attention(4, 1, 64, 64, 0.1, window=70, keep_first=20,
+    "windowed_wide": nk.config(128, 200, [nk.layer("attention", nk.attention(6, 2, 64, 64, 0.1, window=70, keep_first=12,
                                                                               rotation=nk.rot(64, 10000.0, (4.0, 1.0, 4.0, 32))))]),
     "side_by_side": nk.config(64, 200, [nk.layer("parallel", nk.parallel(nk.left(4, 2, 16, 8, 0.3, nk.rot(16, 100.0)), 2, 8, 12, 8.0, 0.7, 1.3))]),
-    "memory_wide": nk.config(128, 200, [nk.layer("parallel", nk.parallel(nk.left(2, 1, 64, 64, 0.1, nk.rot(32, 1000.0)), 3, 40, 50, 12.0, 0.2, 1.5))]),
+    "memory_wide": nk.config(128, 200, [nk.layer("parallel", nk.parallel(nk.left(2, 1, 64, 64, 0.1, nk.rot(32, 1000.0)), 3, 40, 50, 14.0, 0.2, 1.5))]),
     "latent": nk.config(64, 200, [nk.layer("latent_attention", nk.latent(3, 8, 4, 6, 20, 12, 0.4, 1000.0, (2.0, 16, 4.0, 1.0)))]),
     "latent_wide": nk.config(256, 200, [nk.layer("latent_attention", nk.latent(20, 32, 16, 24, 100, 48, 0.1, 10000.0))]),
+    # a latent whose stored head is above the largest the tensor-core kernels take: the generic kernel in both element types
+    "latent_huge": nk.config(128, 200, [nk.layer("latent_attention", nk.latent(2, 16, 8, 12, 262, 20, 0.2, 100.0))]),
     "moe": nk.config(64, 200, [nk.layer("attention", nk.attention(1, 1, 8, 8, 0.5), nk.moe(8, 3, 32, shared=16))]),
     "moe_one": nk.config(64, 200, [nk.layer("attention", nk.attention(1, 1, 8, 8, 0.5), nk.moe(5, 1, 40))]),
 }
@@ -399,7 +401,7 @@ def test_a_memory_remembers_its_first_token_and_a_lost_state_shows(tmp_path):
     implementation says by how much), through portions and single tokens; zeroing the request's state slot between two
     steps moves the logits by far more than the tolerance."""
     from kungfu_b200.engine import StepEntry
-    cfg = nk.config(64, 200, [nk.layer("parallel", nk.parallel(nk.left(1, 1, 8, 8, 0.3), 2, 16, 16, 12.0, 0.05, 1.5))])
+    cfg = nk.config(64, 200, [nk.layer("parallel", nk.parallel(nk.left(1, 1, 8, 8, 0.3), 2, 16, 16, 13.0, 0.05, 1.5))])
     folder = str(tmp_path / "m")
     t = nk.draw_tensors(cfg, 8)
     t["l0.mix.right.f.b"] = torch.full_like(t["l0.mix.right.f.b"], 7.0)
