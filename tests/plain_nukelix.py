@@ -188,6 +188,35 @@ def full_attention(h, w, p: str, m: dict, eps: float, positions):
     return linear(o.reshape(T, -1), w[p + "o"])
 
 
+def memory_walk(q, k, v, gi, gf, state=None):
+    """The memory's recurrence alone.  q, k [T, H, d] (q already times d^-1/2), v [T, H, dv], log gates gi, gf [T, H];
+    `state` (S [H, d, dv], n [H, d], m [H]) from earlier tokens, or None for the start (zeros; m = 0).
+    Returns (o [T, H, dv], state)."""
+    T, H, d = q.shape
+    dv = v.shape[-1]
+    if state is None:
+        state = (torch.zeros(H, d, dv, dtype=F), torch.zeros(H, d, dtype=F), torch.zeros(H, dtype=F))
+    S, n, m = (x.clone().to(F) for x in state)
+    out = torch.zeros(T, H, dv, dtype=F)
+    for a in range(H):
+        top = float(m[a])
+        for t in range(T):
+            new_top = max(float(gf[t, a]) + top, float(gi[t, a]))
+            keep, take = math.exp(float(gf[t, a]) + top - new_top), math.exp(float(gi[t, a]) - new_top)
+            S[a] = keep * S[a] + take * torch.outer(k[t, a], v[t, a])
+            n[a] = keep * n[a] + take * k[t, a]
+            top = new_top
+            den = max(abs(float(n[a] @ q[t, a])), math.exp(-top)) + 1e-6
+            out[t, a] = (S[a].T @ q[t, a]) / den
+        m[a] = top
+    return out, (S, n, m)
+
+
+def memory_gates(zi, zf, cap: float):
+    """Log input gate and log forget gate from their raw values (biases added)."""
+    return cap * torch.tanh(zi / cap), torch.nn.functional.logsigmoid(cap * torch.tanh(zf / cap))
+
+
 def matrix_memory(h, w, p: str, m: dict, eps: float):
     """The right half of the mixer 'parallel': a d x dv memory per head with exponential gates kept stable by a running
     maximum that starts at 0."""
@@ -196,19 +225,8 @@ def matrix_memory(h, w, p: str, m: dict, eps: float):
     q = (linear(h, w[p + "q"]) * d ** -0.5).view(T, H, d)
     k = linear(h, w[p + "k"]).view(T, H, d)
     v = linear(h, w[p + "v"]).view(T, H, dv)
-    gi = cap * torch.tanh(linear(h, w[p + "i"], w[p + "i.b"]) / cap)
-    gf = torch.nn.functional.logsigmoid(cap * torch.tanh(linear(h, w[p + "f"], w[p + "f.b"]) / cap))
-    out = torch.zeros(T, H, dv, dtype=F)
-    for a in range(H):
-        S, n, top = torch.zeros(d, dv, dtype=F), torch.zeros(d, dtype=F), 0.0
-        for t in range(T):
-            new_top = max(float(gf[t, a]) + top, float(gi[t, a]))
-            keep, take = math.exp(float(gf[t, a]) + top - new_top), math.exp(float(gi[t, a]) - new_top)
-            S = keep * S + take * torch.outer(k[t, a], v[t, a])
-            n = keep * n + take * k[t, a]
-            top = new_top
-            den = max(abs(float(n @ q[t, a])), math.exp(-top)) + 1e-6
-            out[t, a] = (S.T @ q[t, a]) / den
+    gi, gf = memory_gates(linear(h, w[p + "i"], w[p + "i.b"]), linear(h, w[p + "f"], w[p + "f.b"]), cap)
+    out, _ = memory_walk(q, k, v, gi, gf)
     o = rms(out, eps).reshape(T, H * dv) * w[p + "norm"].to(F)
     o = o * torch.sigmoid(linear(h, w[p + "g"]))
     return linear(o, w[p + "o"])

@@ -117,6 +117,170 @@ def test_experts_with_the_weight_on_their_input(dtype, T, E, top, W, ff):
     assert float(err.median()) < (1e-5 if dtype == "float32" else 2e-2) and float((err > 0.1).float().mean()) <= (0.0 if dtype == "float32" else 0.05)
 
 
+
+def _step_ctx(rows_of_reqs, slots, pad_rows=0):
+    """A hand-made step: request r has rows_of_reqs[r] consecutive rows and state slot slots[r] (an idle request slot has
+    0 rows); `pad_rows` padding rows (request -1) at the end."""
+    starts, row_req, at = [], [], 0
+    for r, n in enumerate(rows_of_reqs):
+        starts.append(at)
+        row_req += [r] * n
+        at += n
+    row_req += [-1] * pad_rows
+    bufs = {}
+    return types.SimpleNamespace(
+        n_reqs=len(rows_of_reqs), n_rows=len(row_req), row_req=torch.tensor(row_req, dtype=torch.int32, device=DEV),
+        req_row_start=torch.tensor(starts, dtype=torch.int32, device=DEV), req_n_rows=torch.tensor(rows_of_reqs, dtype=torch.int32, device=DEV),
+        req_state_slot=torch.tensor(slots, dtype=torch.int32, device=DEV),
+        buf=lambda tag, shape, dt: bufs.setdefault((tag, tuple(shape), dt), torch.empty(shape, dtype=dt, device=DEV)))
+
+
+@pytest.mark.parametrize("H,d,dv", [(2, 8, 12), (3, 40, 50), (1, 4, 4), (4, 64, 64), (2, 128, 32), (1, 200, 24), (2, 6, 7)])
+def test_matrix_memory_walk_from_earlier_states(H, d, dv):
+    """Three requests with earlier tokens in their states (one with a large running maximum, one fresh), an idle request
+    slot and two padding rows: results and states after a step of unequal portions, and after the same rows one by one."""
+    from kungfu_b200 import ops
+    g = torch.Generator().manual_seed(H * d + dv)
+    rows = [37, 1, 0, 18]
+    slots = [2, 0, -1, 3]
+    T = sum(rows)
+    cap = 9.0
+    width = 2 * H * d + H * dv + 2 * H
+    pad = (-width) % 4
+    proj = torch.randn(T + 2, width + pad, generator=g)
+    proj[:, 2 * H * d + H * dv:] *= 3.0                               # gates that reach the cap
+    bi, bf = 0.5 * torch.randn(H, generator=g), 3.0 + torch.randn(H, generator=g)
+    S0 = torch.randn(4, H, d, dv, generator=g)
+    n0 = torch.zeros(4, H, d + 4)
+    n0[:, :, :d] = torch.randn(4, H, d, generator=g)
+    n0[0, :, d] = 40.0                                                 # a running maximum far from zero
+    n0[2, :, d] = -3.0
+    S0[3], n0[3] = 0.0, 0.0                                            # a fresh request
+    q0, k0, v0, i0, f0 = 0, H * d, 2 * H * d, 2 * H * d + H * dv, 2 * H * d + H * dv + H
+
+    def reference(r, row0, n, state):
+        x = proj[row0:row0 + n].double()
+        gi, gf = pn.memory_gates(x[:, i0:i0 + H] + bi.double(), x[:, f0:f0 + H] + bf.double(), cap)
+        return pn.memory_walk(x[:, q0:q0 + H * d].view(n, H, d) * d ** -0.5, x[:, k0:k0 + H * d].view(n, H, d),
+                              x[:, v0:v0 + H * dv].view(n, H, dv), gi, gf, state)
+
+    for one_by_one in (False, True):
+        S, nst = S0.clone().to(DEV), n0.clone().to(DEV)
+        out = torch.zeros(T + 2, H * dv, device=DEV)
+        if not one_by_one:
+            ops.mlstm(proj.to(DEV), q0, k0, v0, i0, f0, bi.to(DEV), bf.to(DEV), cap, S, nst, out, H, d, dv, _step_ctx(rows, slots, 2))
+        else:
+            starts = [0, 37, 38, 38]
+            for step in range(max(rows)):
+                live = [r for r in range(4) if step < rows[r]]
+                ctx = _step_ctx([1] * len(live), [slots[r] for r in live])
+                pick = torch.tensor([starts[r] + step for r in live])
+                o = torch.zeros(len(live), H * dv, device=DEV)
+                ops.mlstm(proj[pick].contiguous().to(DEV), q0, k0, v0, i0, f0, bi.to(DEV), bf.to(DEV), cap, S, nst, o, H, d, dv, ctx)
+                out[pick.to(DEV)] = o
+        torch.cuda.synchronize()
+        at = 0
+        for r, n in enumerate(rows):
+            if n == 0:
+                continue
+            sl = slots[r]
+            ref, (Sr, nr, mr) = reference(r, at, n, (S0[sl], n0[sl, :, :d], n0[sl, :, d]))
+            assert _rel(out[at:at + n].view(n, H, dv), ref) < 2e-5, (r, one_by_one)
+            # the state in the stabiliser's own units: exp(m) S and exp(m) n are what the design defines
+            got_S = S[sl].double().cpu() * torch.exp(nst[sl, :, d].double().cpu() - mr)[:, None, None]
+            assert _rel(got_S, Sr) < 2e-5 and float((nst[sl, :, d].cpu() - mr).abs().max()) < 1e-3
+            at += n
+        assert float(out[T:].abs().max()) == 0.0 and torch.equal(S[1].cpu(), S0[1])          # padding rows, the idle slot
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("nh,nkv,dk,dv,rot,interleaved,P", [(4, 2, 16, 24, 8, True, 4), (3, 3, 8, 8, 8, False, 8), (8, 2, 64, 64, 32, True, 64),
+                                                           (2, 1, 20, 10, 0, False, 16), (5, 5, 10, 6, 6, True, 16), (4, 4, 128, 64, 128, False, 64)])
+def test_projections_normed_over_all_heads_turned_mixed_and_filed(dtype, nh, nkv, dk, dv, rot, interleaved, P):
+    """q|k|v with biases -> the norms over the whole projections, rotation in either pairing, value mixing in both roles ->
+    q rows and the pages, for two requests in the middle of their sequences and a padding row."""
+    from kungfu_b200 import ops
+    tdt = DTYPES[dtype]
+    tol = 1e-5 if dtype == "float32" else 1e-2
+    g = torch.Generator().manual_seed(nh * dk + dv)
+    positions = [5, 6, 7, 8, 9, 10, 11, 30, 0]
+    row_req = [0] * 7 + [1, -1]
+    T = len(positions)
+    D = ops.attention_head_size(max(dk, dv))
+    C = (nh + nkv) * dk + nkv * dv
+    ld = C + 4 + (-C) % 4
+    proj = torch.randn(T, ld, generator=g)
+    bias = (0.3 * torch.randn(C, generator=g)).to(tdt)
+    wq, wk = (1 + 0.3 * torch.randn(nh * dk, generator=g)).to(tdt), (1 + 0.3 * torch.randn(nkv * dk, generator=g)).to(tdt)
+    lam = torch.tensor([0.35]).to(tdt)
+    first = torch.randn(T, nkv * dv, generator=g)
+    freqs = pn.plain_frequencies({"base": 50.0, "dims": max(rot, 2)})[: rot // 2]
+    ang = torch.tensor(positions, dtype=torch.float64)[:, None] * freqs[None, :]
+    cos, sin = torch.cos(ang).float().to(DEV), torch.sin(ang).float().to(DEV)
+    n_pages = 2 * (40 // P + 2)
+    table = torch.arange(n_pages, dtype=torch.int32).view(2, -1)
+    table = table.flip(1).contiguous().to(DEV)
+    ctx = types.SimpleNamespace(positions=torch.tensor(positions, dtype=torch.int32, device=DEV),
+                                row_req=torch.tensor(row_req, dtype=torch.int32, device=DEV), block_tables=[table])
+    x = proj[:, :C].double() + bias.double()
+    q = pn.rms(x[:, :nh * dk], 1e-5) * wq.double()
+    k = pn.rms(x[:, nh * dk:(nh + nkv) * dk], 1e-5) * wk.double()
+    v = x[:, (nh + nkv) * dk:]
+    pos_t = torch.tensor(positions)
+    q = pn.rotate(q.view(T, nh, dk), pos_t, freqs, rot, interleaved, 1.25)
+    k = pn.rotate(k.view(T, nkv, dk), pos_t, freqs, rot, interleaved, 1.25)
+    for mode in (0, 1, 2):
+        pages = torch.full((n_pages, 2, nkv, P, D), 7.0, dtype=tdt, device=DEV)
+        cache = types.SimpleNamespace(pages=pages, page_size=P, group=0, writes=True)
+        q_out = torch.full((T, nh * D), 7.0, dtype=tdt, device=DEV)
+        shared = first.clone().to(DEV)
+        ops.rownorm_rope_append(proj.to(DEV), 0, bias.to(DEV), wq.to(DEV), wk.to(DEV), 1e-5, cos if rot else None, sin if rot else None,
+                                rot, interleaved, 1.25, nh, nkv, dk, dv, ctx, cache, q_out, v_mix=lam.to(DEV) if mode == 2 else None,
+                                v_shared=shared if mode else None, v_mode=mode)
+        torch.cuda.synchronize()
+        want_v = v if mode != 2 else (1 - float(lam)) * v + float(lam) * first.double()
+        qo = q_out.view(T, nh, D)
+        assert _rel(qo[:8, :, :dk], q[:8]) < tol and float(qo[:8, :, dk:].abs().max() if D > dk else 0.0) == 0.0
+        assert float(qo[8].abs().max()) == 0.0                          # the padding row's queries are zero
+        for t in range(8):
+            page = int(table[row_req[t], positions[t] // P])
+            kk, vv = pages[page, 0, :, positions[t] % P], pages[page, 1, :, positions[t] % P]
+            assert _rel(kk[:, :dk], k[t]) < tol and _rel(vv[:, :dv], want_v[t].view(nkv, dv)) < tol
+            assert float(kk[:, dk:].abs().max() if D > dk else 0.0) == 0.0 and float(vv[:, dv:].abs().max() if D > dv else 0.0) == 0.0
+        if mode == 1:
+            assert _rel(shared[:8], v[:8]) < 1e-6                       # the first mixing layer leaves its values for the others
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("T,W", [(5, 64), (300, 512), (37, 100), (260, 2048)])
+def test_sum_norm_and_copy_in_one_kernel(dtype, T, W):
+    from kungfu_b200 import ops
+    tdt = DTYPES[dtype]
+    g = torch.Generator().manual_seed(T + W)
+    res, branch = torch.randn(T, W, generator=g), 2.0 * torch.randn(T, W, generator=g)
+    w = (1 + 0.3 * torch.randn(W, generator=g)).to(tdt)
+    rd, copy = res.to(DEV), torch.empty(T, W, dtype=tdt, device=DEV)
+    ops.add_rmsnorm(branch.to(DEV), w.to(DEV), 1e-5, False, rd, copy_out=copy)
+    ref = res.double() + pn.rms(branch.double(), 1e-5) * w.double()
+    assert _rel(rd, ref) < 2e-6 and _rel(copy, ref) < (2e-6 if dtype == "float32" else 1e-2)
+
+
+def test_head_norm_with_one_weight_vector_per_head():
+    from kungfu_b200 import ops
+    g = torch.Generator().manual_seed(3)
+    T, H, dv = 9, 3, 20
+    o, gate = torch.randn(T, H * dv, generator=g), torch.randn(T, H * dv + 8, generator=g)
+    w = 1 + 0.3 * torch.randn(H * dv, generator=g)
+    out = torch.empty(T, H * dv, device=DEV)
+    ops.head_norm_gate(o.to(DEV), w.to(DEV), 1e-5, gate.to(DEV), 8, "sigmoid", out, H, dv)
+    ref = (pn.rms(o.double().view(T, H, dv), 1e-5).reshape(T, H * dv) * w.double()) * torch.sigmoid(gate[:, 8:].double())
+    assert _rel(out, ref) < 1e-5
+    shared = 1 + 0.3 * torch.randn(dv, generator=g)
+    ops.head_norm_gate(o.to(DEV), shared.to(DEV), 1e-5, gate.to(DEV), 8, "sigmoid", out, H, dv)
+    ref = (pn.rms(o.double().view(T, H, dv), 1e-5) * shared.double()).reshape(T, H * dv) * torch.sigmoid(gate[:, 8:].double())
+    assert _rel(out, ref) < 1e-5
+
+
 # ---- models ------------------------------------------------------------------------------------------------------------
 
 def _runner(folder, dtype, page, max_tokens, max_requests=4, graphs=True, ctx=2048):
