@@ -91,6 +91,49 @@ def test_attention_with_kept_first_tokens_and_a_sink(dtype, H, G, D, P, window, 
         assert _rel(out.view(T, H, D), ref[rows]) < (2e-5 if dtype == "float32" else 2e-2), (rows[0], T)
 
 
+@pytest.mark.parametrize("H,G,D,window,keep,sink", [(4, 2, 64, 900, 70, True), (4, 1, 128, 500, 200, True), (2, 2, 64, None, 0, True),
+                                                    (8, 2, 64, 700, 0, True), (4, 4, 256, 300, 64, False)])
+@pytest.mark.parametrize("plan", [None, (4, 0), (3, 2), (8, 0)])
+def test_long_contexts_whose_keys_are_cut_into_runs(H, G, D, window, keep, sink, plan, monkeypatch):
+    """Short portions and single rows at a context of 1,500 tokens on the tensor-core kernels: the prompt kernel cuts a
+    tile's keys into several runs (planned, and forced to 3, 4 and 8), the decode kernel into several splits; the kept
+    tokens lie in the first run and the sink is counted once."""
+    from kungfu_b200 import ops
+    monkeypatch.setattr(ops, "prefill_plan_override", plan)
+    slow_before = ops.fallback_count()
+    g = torch.Generator().manual_seed(H * D + (window or 0))
+    n, P = 1500, 64
+    q, k, v = (torch.randn(n, h, D, generator=g).to(torch.bfloat16).double() for h in (H, G, G))
+    q[:, :, :] *= 1.5                                               # sharp rows: a few keys carry each
+    scale = 2.0 / D ** 0.5
+    ref = pn.attend(q, k, v, scale, pn.visible(n, window, keep), sink)
+    pages, table = _paged(k, v, P, torch.bfloat16)
+    for rows in (list(range(1400, 1437)), list(range(1200, 1500)), [1499], [1024]):
+        T = len(rows)
+        single = T == 1
+        ctx = types.SimpleNamespace(
+            positions=torch.tensor(rows, dtype=torch.int32, device=DEV), row_req=torch.zeros(T, dtype=torch.int32, device=DEV),
+            block_tables=[table], max_kv_len=rows[-1] + 1, n_rows=T, n_dec_rows=T if single else 0, n_pre_rows=0 if single else T,
+            dec_rows=None, pre_rows=None, n_tiles=0, n_wide=0)
+        if not single:
+            ctx.pre_rows = torch.arange(T, dtype=torch.int32, device=DEV)
+            bounds, wide = list(range(0, T, 64)), list(range(0, T, 128))
+            ctx.tile_row0 = torch.tensor(bounds, dtype=torch.int32, device=DEV)
+            ctx.tile_nrows = torch.tensor([min(64, T - b) for b in bounds], dtype=torch.int32, device=DEV)
+            ctx.n_tiles = len(bounds)
+            ctx.wide_row0 = torch.tensor(wide, dtype=torch.int32, device=DEV)
+            ctx.wide_nrows = torch.tensor([min(128, T - b) for b in wide], dtype=torch.int32, device=DEV)
+            ctx.n_wide = len(wide)
+        cache = types.SimpleNamespace(pages=pages, page_size=P, group=0, writes=True)
+        out = torch.empty(T, H * D, dtype=torch.bfloat16, device=DEV)
+        ops.paged_attention(q[rows].to(torch.bfloat16).reshape(T, H * D).to(DEV), out, ctx, cache, H, G, D, scale, 0.0, window,
+                            keep_first=keep, sink=sink)
+        torch.cuda.synchronize()
+        ops.raise_on_device_error(torch.device(DEV))
+        assert _rel(out.view(T, H, D), ref[rows]) < 2e-2, (rows[0], T)
+    assert ops.fallback_count() == slow_before                      # every launch ran a tensor-core kernel
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("T,E,top,W,ff", [(1, 8, 2, 64, 32), (37, 6, 3, 100, 30), (300, 16, 4, 512, 256), (130, 3, 3, 200, 72)])
 def test_experts_with_the_weight_on_their_input(dtype, T, E, top, W, ff):
