@@ -937,7 +937,7 @@ def micro_memory() -> int:
             req_state_slot=torch.arange(reqs, dtype=torch.int32, device=device),
             buf=lambda tag, shape, dt: bufs.setdefault(tag, torch.empty(shape, dtype=dt, device=device)))
         memory = torch.zeros(reqs, H, d, dv, device=device)
-        norm_state = torch.zeros(reqs, H, d + 4, device=device)
+        norm_state = torch.zeros(reqs, H, ops.mlstm_norm_width(d, dv), device=device)
         bias = torch.zeros(H, device=device, dtype=torch.bfloat16)
         out = torch.empty(rows, H * dv, device=device)
         run = lambda: ops.mlstm(proj, 0, H * d, 2 * H * d, 2 * H * d + 2 * H * dv, 2 * H * d + 2 * H * dv + H, bias, bias + 4.0, 15.0,

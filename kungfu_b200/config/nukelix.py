@@ -279,7 +279,7 @@ class NukelixConfig:
 
     def state_summary(self, element_size: int = 2) -> list:
         """Per layer, what it keeps per request: bytes per token of its pages, the window that bounds them, fixed bytes."""
-        from ..ops import attention_head_size
+        from ..ops import attention_head_size, mlstm_norm_width
         from ..parts.latent import latent_head_size
         out = []
         for i, l in enumerate(self.layers):
@@ -291,7 +291,7 @@ class NukelixConfig:
             a = m if l.type == ATTENTION else m.left
             fixed = 0
             if l.type == PARALLEL:
-                fixed = 4 * m.right.heads * (m.right.dim * m.right.vdim + m.right.dim + 4)
+                fixed = 4 * m.right.heads * (m.right.dim * m.right.vdim + mlstm_norm_width(m.right.dim, m.right.vdim))
             out.append({"layer": i, "kind": "kv_pages" if not fixed else "kv_pages+memory", "window": a.window,
                         "fixed_bytes": fixed,
                         "bytes_per_token": 2 * a.kv_heads * attention_head_size(max(a.dim, a.vdim)) * element_size})

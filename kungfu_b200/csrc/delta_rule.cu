@@ -277,7 +277,7 @@ KF_API int kf_delta_rule(const float* qkv, int ld_qkv, int q0, int k0, int v0, c
 template <typename TW, typename TO>
 __global__ void head_norm_gate_kernel(const float* __restrict__ o, const TW* __restrict__ w, float eps,
                                       const float* __restrict__ gate, int ld_gate, int gate0, int act,
-                                      TO* __restrict__ out, int H, int dv, int T, int w_stride) {
+                                      TO* __restrict__ out, int H, int dv, int T, int w_stride, int ldo, int ocol0, float scale) {
   kf_pdl_trigger();
   kf_pdl_wait();
   const int lane = threadIdx.x & 31;
@@ -293,16 +293,19 @@ __global__ void head_norm_gate_kernel(const float* __restrict__ o, const TW* __r
   for (int i = lane; i < dv; i += 32) {
     const float z = g[i];
     const float s = 1.f / (1.f + expf(-z));
-    kf_store(out, ((size_t)t * H + h) * dv + i, src[i] * inv * kf_load(w, h * w_stride + i) * (act == 0 ? z * s : s));
+    kf_store(out, (size_t)t * ldo + ocol0 + h * dv + i, src[i] * inv * kf_load(w, h * w_stride + i) * (act == 0 ? z * s : s) * scale);
   }
 }
 
 KF_API int kf_head_norm_gate(const float* o, const void* w, int w_dtype, float eps, const float* gate, int ld_gate, int gate0,
-                             int act, void* out, int out_dtype, int H, int dv, int T, int w_stride, cudaStream_t stream) {
+                             int act, void* out, int out_dtype, int H, int dv, int T, int w_stride, int ldo, int ocol0, float scale,
+                             cudaStream_t stream) {
   if (T <= 0) return KF_OK;
+  if (ldo <= 0) ldo = H * dv;                   // rows of `out` hold the heads alone
+  if (ocol0 < 0 || ocol0 + H * dv > ldo) return KF_ERR_SIZE;
   const dim3 grid(kf_ceil_div((long)T * H, 4));
 #define KF_GO(TW, TO) \
-  kf_launch(head_norm_gate_kernel<TW, TO>, grid, dim3(128), 0, stream, o, (const TW*)w, eps, gate, ld_gate, gate0, act, (TO*)out, H, dv, T, w_stride)
+  kf_launch(head_norm_gate_kernel<TW, TO>, grid, dim3(128), 0, stream, o, (const TW*)w, eps, gate, ld_gate, gate0, act, (TO*)out, H, dv, T, w_stride, ldo, ocol0, scale)
   if (w_dtype == KF_F32 && out_dtype == KF_F32) KF_GO(float, float);
   else if (w_dtype == KF_BF16 && out_dtype == KF_BF16) KF_GO(__nv_bfloat16, __nv_bfloat16);
   else if (w_dtype == KF_BF16 && out_dtype == KF_F32) KF_GO(__nv_bfloat16, float);

@@ -7,6 +7,10 @@
 //   m' = max(gf + m, gi);   keep = exp(gf + m - m'),  take = exp(gi - m'),  floor = exp(-m')
 //   S' = keep S + take k v^T;   n' = keep n + take k;   o = S'^T q / (max(|n' . q|, floor) + 1e-6),   q times d^-1/2
 // m starts at 0 (a zeroed state slot), S and n at zero.
+// State per (slot, head): S [d, dv]; and a row of ceil(dv / 16) copies of n (d numbers each) followed by m and three unused
+// numbers.  Every block of the walk owns 16 value columns and ITS OWN copy of n, which it reads at its start and writes at
+// its end: blocks of one head run at different times, and a shared n would be read by a late block after an early one had
+// already moved it on.
 //
 // kf_mlstm_gates: one warp per (request, head) walks the request's rows 32 at a time.  Inside a chunk the maxima follow
 //   from two scans: with F_j the running sum of gf, m_j = F_j + max(m_before, max_{s <= j}(gi_s - F_s)).  Any rounding of
@@ -103,7 +107,7 @@ KF_API int kf_mlstm_gates(const float* proj, int ld, int i0, int f0, const void*
 struct KfMlstmArgs {
   const float* proj; int ld, q0, k0, v0;       // 32-bit rows: q (H d), k (H d), v (H dv) column ranges
   const float* gates;                          // [rows, H] of (keep, take, floor, m)
-  float* S; float* nstate; int nstride;        // [slots, H, d, dv]; [slots, H, nstride] with n in the first d places
+  float* S; float* nstate; int nstride;        // [slots, H, d, dv]; [slots, H, nstride]: a copy of n per block of 16 columns
   float* out;                                  // [rows, H dv]
   int H, d, dv, n_reqs;
   float q_scale;
@@ -139,7 +143,7 @@ __global__ void __launch_bounds__(LANES * ML_COLS) mlstm_scan_kernel(KfMlstmArgs
   const int d = p.d, dv = p.dv;
   float S[R], nn[R];
   float* Sg = p.S + ((size_t)slot * p.H + h) * d * dv;
-  float* ng = p.nstate + ((size_t)slot * p.H + h) * p.nstride;
+  float* ng = p.nstate + ((size_t)slot * p.H + h) * p.nstride + (size_t)cb * d;      // this block's own copy of n
   auto row_of = [&](int k) { return ((k >> 2) * LANES + l) * 4 + (k & 3); };
 #pragma unroll
   for (int k = 0; k < R; ++k) {
@@ -237,7 +241,7 @@ __global__ void __launch_bounds__(LANES * ML_COLS) mlstm_scan_kernel(KfMlstmArgs
   for (int k = 0; k < R; ++k) {
     const int row = row_of(k);
     if (live && row < d) Sg[(size_t)row * dv + col] = S[k];
-    if (cb == 0 && cl == 0 && row < d) ng[row] = nn[k];
+    if (cl == 0 && row < d) ng[row] = nn[k];
   }
 }
 
@@ -245,7 +249,7 @@ KF_API int kf_mlstm_scan(const float* proj, int ld, int q0, int k0, int v0, cons
                          int nstride, float* out, int H, int d, int dv, float q_scale, int n_reqs, const int* req_row_start,
                          const int* req_n_rows, const int* req_state_slot, int writes, cudaStream_t stream) {
   if (n_reqs <= 0) return KF_OK;
-  if (d < 1 || d > 256 || dv < 1 || H < 1 || nstride < d) return KF_ERR_SIZE;
+  if (d < 1 || d > 256 || dv < 1 || H < 1 || nstride < ((dv + ML_COLS - 1) / ML_COLS) * d) return KF_ERR_SIZE;
   KfMlstmArgs p{proj, ld, q0, k0, v0, gates, S, nstate, nstride, out, H, d, dv, n_reqs, q_scale, req_row_start, req_n_rows,
                 req_state_slot, writes};
   const int col_blocks = (dv + ML_COLS - 1) / ML_COLS;

@@ -277,7 +277,7 @@ KF_API int kf_qkv_prepare_commits_inline(int ld, int col0, int rot, int interlea
 // g read from column gcol0 + h of a 32-bit matrix with ld columns (null: no gate, only the packing).
 template <typename TQ>
 __global__ void head_gate_kernel(const TQ* __restrict__ o, const float* __restrict__ g, int ld, int gcol0, int nh, int dv,
-                                 int D, TQ* __restrict__ out, const int* __restrict__ row_req) {
+                                 int D, TQ* __restrict__ out, const int* __restrict__ row_req, int ldo, int ocol0, float scale) {
   kf_pdl_trigger();
   kf_pdl_wait();
   const int t = blockIdx.x;
@@ -288,14 +288,16 @@ __global__ void head_gate_kernel(const TQ* __restrict__ o, const float* __restri
     if (!pad) {
       v = kf_load(o, ((size_t)t * nh + h) * D + i);
       if (g) v *= 1.f / (1.f + expf(-g[(size_t)t * ld + gcol0 + h]));
+      v *= scale;
     }
-    kf_store(out, (size_t)t * nh * dv + e, v);
+    kf_store(out, (size_t)t * ldo + ocol0 + e, v);
   }
 }
 
 // Eight elements per thread (one 16-byte load of bfloat16), the gate computed once for them.
 __global__ void head_gate_vec_kernel(const __nv_bfloat16* __restrict__ o, const float* __restrict__ g, int ld, int gcol0, int nh,
-                                     int dv, int D, __nv_bfloat16* __restrict__ out, const int* __restrict__ row_req) {
+                                     int dv, int D, __nv_bfloat16* __restrict__ out, const int* __restrict__ row_req, int ldo,
+                                     int ocol0, float scale) {
   kf_pdl_trigger();
   kf_pdl_wait();
   const int t = blockIdx.x;
@@ -305,8 +307,8 @@ __global__ void head_gate_vec_kernel(const __nv_bfloat16* __restrict__ o, const 
     uint4 raw = make_uint4(0u, 0u, 0u, 0u);
     if (!pad) {
       raw = *reinterpret_cast<const uint4*>(o + ((size_t)t * nh + h) * D + i);
-      if (g) {
-        const float s = 1.f / (1.f + expf(-g[(size_t)t * ld + gcol0 + h]));
+      if (g || scale != 1.f) {
+        const float s = (g ? 1.f / (1.f + expf(-g[(size_t)t * ld + gcol0 + h])) : 1.f) * scale;
         __nv_bfloat162* pr = reinterpret_cast<__nv_bfloat162*>(&raw);
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
@@ -315,25 +317,27 @@ __global__ void head_gate_vec_kernel(const __nv_bfloat16* __restrict__ o, const 
         }
       }
     }
-    *reinterpret_cast<uint4*>(out + (size_t)t * nh * dv + e) = raw;
+    *reinterpret_cast<uint4*>(out + (size_t)t * ldo + ocol0 + e) = raw;
   }
 }
 
 KF_API int kf_head_gate(const void* o, const float* g, int ld, int gcol0, int nh, int dv, int D, void* out, int dtype,
-                        const int* row_req, int T, cudaStream_t stream) {
+                        const int* row_req, int T, int ldo, int ocol0, float scale, cudaStream_t stream) {
   if (T <= 0) return KF_OK;
+  if (ldo <= 0) ldo = nh * dv;                  // rows of `out` hold the heads alone
+  if (ocol0 < 0 || ocol0 + nh * dv > ldo) return KF_ERR_SIZE;
   const int threads = nh * dv >= 1024 ? 256 : 128;
-  if (dtype == KF_BF16 && dv % 8 == 0 && D % 8 == 0 && (((uintptr_t)o | (uintptr_t)out) & 15) == 0) {
+  if (dtype == KF_BF16 && dv % 8 == 0 && D % 8 == 0 && ldo % 8 == 0 && ocol0 % 8 == 0 && (((uintptr_t)o | (uintptr_t)out) & 15) == 0) {
     kf_launch(head_gate_vec_kernel, dim3(T), dim3(nh * dv >= 2048 ? 256 : 128), 0, stream, (const __nv_bfloat16*)o, g, ld, gcol0, nh,
-              dv, D, (__nv_bfloat16*)out, row_req);
+              dv, D, (__nv_bfloat16*)out, row_req, ldo, ocol0, scale);
     KF_CHECK_LAUNCH();
     return KF_OK;
   }
   if (dtype == KF_F32)
-    kf_launch(head_gate_kernel<float>, dim3(T), dim3(threads), 0, stream, (const float*)o, g, ld, gcol0, nh, dv, D, (float*)out, row_req);
+    kf_launch(head_gate_kernel<float>, dim3(T), dim3(threads), 0, stream, (const float*)o, g, ld, gcol0, nh, dv, D, (float*)out, row_req, ldo, ocol0, scale);
   else if (dtype == KF_BF16)
     kf_launch(head_gate_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, stream, (const __nv_bfloat16*)o, g, ld, gcol0, nh, dv, D,
-              (__nv_bfloat16*)out, row_req);
+              (__nv_bfloat16*)out, row_req, ldo, ocol0, scale);
   else
     return KF_ERR_DTYPE;
   KF_CHECK_LAUNCH();

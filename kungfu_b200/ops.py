@@ -671,11 +671,14 @@ def qkv_prepare(proj, col0: int, in_bias, conv_w, conv_state, q_norm, k_norm, ep
 
 
 @_dispatch("head_gate")
-def head_gate(o, proj, gate_col0: int, n_heads: int, value_dim: int, head_dim: int, out, ctx) -> None:
-    """out[t, h * value_dim + i] = o[t, h * head_dim + i] * sigmoid(proj[t, gate_col0 + h]); proj None: packing only."""
+def head_gate(o, proj, gate_col0: int, n_heads: int, value_dim: int, head_dim: int, out, ctx, out_col0: int = 0,
+              scale: float = 1.0) -> None:
+    """out[t, out_col0 + h * value_dim + i] = o[t, h * head_dim + i] * sigmoid(proj[t, gate_col0 + h]) * scale; proj None:
+    packing (and the factor) only.  `out` may be wider than the heads (the joined input of one output product)."""
     T = out.shape[0]
     _check(library().kf_head_gate(_p(o), _p(proj), proj.shape[1] if proj is not None else 0, int(gate_col0), n_heads,
-                                  value_dim, head_dim, _p(out), _dt(out), _p(ctx.row_req), T, _stream()), "head_gate")
+                                  value_dim, head_dim, _p(out), _dt(out), _p(ctx.row_req), T, out.shape[1], int(out_col0),
+                                  _f(scale), _stream()), "head_gate")
 
 
 chunked_scan = True          # False: a long prompt's recurrence is walked by one block per (request, head, 32 columns) only
@@ -835,15 +838,18 @@ _GATE_ACT = {"silu": 0, "sigmoid": 1}
 
 
 @_dispatch("head_norm_gate")
-def head_norm_gate(o, weight, eps: float, gate, gate0: int, act: str, out, heads: int, vdim: int) -> None:
-    """out[t, h, :] = o[t, h, :] / rms(o[t, h, :]) * weight * act(gate[t, gate0 + h * vdim + :]); act silu or sigmoid.
-    `weight` holds vdim numbers (shared by the heads) or heads * vdim (one vector per head)."""
+def head_norm_gate(o, weight, eps: float, gate, gate0: int, act: str, out, heads: int, vdim: int, out_col0: int = 0,
+                   scale: float = 1.0) -> None:
+    """out[t, out_col0 + h * vdim + :] = o[t, h, :] / rms(o[t, h, :]) * weight * act(gate[t, gate0 + h * vdim + :]) * scale;
+    act silu or sigmoid.  `weight` holds vdim numbers (shared by the heads) or heads * vdim (one vector per head); `out` may
+    be wider than the heads (the joined input of one output product)."""
     T = out.shape[0]
     if weight.numel() not in (vdim, heads * vdim):
         raise KernelError(f"head_norm_gate: {weight.numel()} weights for {heads} heads of {vdim}")
     w_stride = vdim if (weight.numel() == heads * vdim and heads > 1) else 0
     _check(library().kf_head_norm_gate(_p(o), _p(weight), _dt(weight), _f(eps), _p(gate), gate.shape[1], int(gate0),
-                                       _GATE_ACT[act], _p(out), _dt(out), heads, vdim, T, w_stride, _stream()), "head_norm_gate")
+                                       _GATE_ACT[act], _p(out), _dt(out), heads, vdim, T, w_stride, out.shape[1], int(out_col0),
+                                       _f(scale), _stream()), "head_norm_gate")
 
 
 @_dispatch("latent_append")
@@ -909,21 +915,33 @@ def rownorm_rope_append(proj, col0: int, bias, q_norm, k_norm, eps: float, cos, 
                                             _stream()), "rownorm_rope_append")
 
 
+MLSTM_COLUMNS = 16          # value columns a block of the matrix memory's walk owns
+
+
+def mlstm_norm_width(dim: int, vdim: int) -> int:
+    """Numbers per head in the matrix memory's second state: a copy of n (dim numbers) per block of MLSTM_COLUMNS value
+    columns, then m and three unused numbers."""
+    return -(-int(vdim) // MLSTM_COLUMNS) * int(dim) + 4
+
+
 @_dispatch("mlstm")
 def mlstm(proj, q0: int, k0: int, v0: int, i0: int, f0: int, bias_i, bias_f, cap: float, memory, norm_state, out, heads: int,
           dim: int, vdim: int, ctx, writes: bool = True) -> None:
     """The matrix memory with exponential gates over the rows of every request of the step, from and into `memory`
-    [requests, heads, dim, vdim] and `norm_state` [requests, heads, dim + 4] (n in the first dim places, the running
-    maximum m at place dim), both 32-bit.  q, k, v and the raw gates are column ranges of `proj` (32-bit); q is
+    [requests, heads, dim, vdim] and `norm_state` [requests, heads, mlstm_norm_width(dim, vdim)] (one copy of n per 16 value
+    columns, each owned by the block that walks those columns, then the running maximum m), both 32-bit.  q, k, v and the raw gates are column ranges of `proj` (32-bit); q is
     multiplied by dim^-1/2.  gi = cap tanh((zi + bias_i) / cap), gf = logsigmoid(cap tanh((zf + bias_f) / cap));
     m' = max(gf + m, gi); S' = exp(gf + m - m') S + exp(gi - m') k v^T, n' likewise with k;
     out = S'^T q / (max(|n' . q|, exp(-m')) + 1e-6), 32-bit [rows, heads * vdim]."""
     T = out.shape[0]
     lib = library()
+    m_at = mlstm_norm_width(dim, vdim) - 4
+    if norm_state.shape[2] != m_at + 4:
+        raise KernelError(f"mlstm: norm_state rows of {norm_state.shape[2]} numbers, expected {m_at + 4}")
     gates = ctx.buf("mlstm_gates", (T * heads * 4,), torch.float32)
     wdt = _dt(bias_i) if bias_i is not None else F32
     _check(lib.kf_mlstm_gates(_p(proj), proj.shape[1], int(i0), int(f0), _p(bias_i), _p(bias_f), wdt, _f(cap), _p(norm_state),
-                              norm_state.shape[2], int(dim), _p(gates), heads, ctx.n_reqs, _p(ctx.req_row_start),
+                              norm_state.shape[2], int(m_at), _p(gates), heads, ctx.n_reqs, _p(ctx.req_row_start),
                               _p(ctx.req_n_rows), _p(ctx.req_state_slot), int(writes), _stream()), "mlstm (gates)")
     _check(lib.kf_mlstm_scan(_p(proj), proj.shape[1], int(q0), int(k0), int(v0), _p(gates), _p(memory), _p(norm_state),
                              norm_state.shape[2], _p(out), heads, dim, vdim, _f(float(dim) ** -0.5), ctx.n_reqs,

@@ -296,10 +296,22 @@ class RowNormAttention(Mixer):
         return PagedKV(self.n_kv_heads, self.head_dim, self.window, self.keep_first)
 
     def forward(self, x, ctx, cache):
-        T = x.shape[0]
-        nh, nkv, D = self.n_heads, self.n_kv_heads, self.head_dim
-        proj = ctx.buf("attn_proj", (T, self.proj_width), torch.float32)
+        proj = ctx.buf("attn_proj", (x.shape[0], self.proj_width), torch.float32)
         ops.linear(x, self.w_in, proj)
+        return self.forward_projected(proj, 0, ctx, cache)
+
+    @property
+    def heads_width(self) -> int:
+        """Columns of the output product's input (the gated heads)."""
+        return self.n_heads * self.value_dim
+
+    def forward_projected(self, proj, col0: int, ctx, cache, heads_out=None, out_col0: int = 0, scale: float = 1.0):
+        """The mixer from its stacked projection's 32-bit result, which starts at column `col0` of `proj` (a mixer that
+        stands beside another one shares one product over both stacked matrices).  With `heads_out` the mixer stops before
+        its output product and leaves its gated heads, times `scale`, in columns `out_col0`.. of that buffer (the other
+        mixer's follow, and one product over both output matrices side by side gives the weighted sum)."""
+        T = proj.shape[0]
+        nh, nkv, D = self.n_heads, self.n_kv_heads, self.head_dim
         if self.position is not None:
             cos, sin = self.position.rotation(ctx)
             rot, interleaved = 2 * cos.shape[1], bool(getattr(self.position, "interleaved", False))
@@ -312,15 +324,19 @@ class RowNormAttention(Mixer):
         if self.v_mix is not None:
             shared = ctx.buf(f"attn_{self.v_mix_tag}", (T, nkv * self.value_dim), torch.float32)
             mode = 1 if self.v_mix == "first" else 2
-        ops.rownorm_rope_append(proj, 0, self.bias, self.q_norm, self.k_norm, self.norm_eps, cos, sin, rot, interleaved, mag,
+        ops.rownorm_rope_append(proj, col0, self.bias, self.q_norm, self.k_norm, self.norm_eps, cos, sin, rot, interleaved, mag,
                                 nh, nkv, self.key_dim, self.value_dim, ctx, cache, q,
                                 v_mix=self.v_mix_weight if mode == 2 else None, v_shared=shared, v_mode=mode)
         o = ctx.buf("attn_o", (T, nh * D), ctx.act_dtype)
         ops.paged_attention(q, o, ctx, cache, nh, nkv, D, self.scale, 0.0, self.window, keep_first=self.keep_first,
                             sink=self.sink)
+        if heads_out is not None:                      # the gated heads, times `scale`, into a row another product reads
+            ops.head_gate(o, proj if self.gated else None, col0 + self.qkv_width, nh, self.value_dim, D, heads_out, ctx,
+                          out_col0=out_col0, scale=scale)
+            return None
         if self.gated or D != self.value_dim:
             packed = ctx.buf("attn_gated", (T, nh * self.value_dim), ctx.act_dtype)
-            ops.head_gate(o, proj if self.gated else None, self.qkv_width, nh, self.value_dim, D, packed, ctx)
+            ops.head_gate(o, proj if self.gated else None, col0 + self.qkv_width, nh, self.value_dim, D, packed, ctx)
             o = packed
         y = ctx.buf(self.out_tag, (T, self.width), torch.float32)
         ops.linear(o, self.wo, y)

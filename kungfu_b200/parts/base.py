@@ -93,8 +93,10 @@ class Part:
         seen = set() if seen is None else seen
         n = 0
         for w in self.weights():
-            if w.data_ptr() not in seen:
-                seen.add(w.data_ptr())
+            # by storage: a view of a stacked matrix that another part holds whole is not counted again
+            key = w.untyped_storage().data_ptr() if w.numel() else w.data_ptr()
+            if key not in seen:
+                seen.add(key)
                 n += w.numel() * w.element_size()
         for c in self.children():
             n += c.weight_bytes(seen)

@@ -219,13 +219,13 @@ class CpuOps:
             cache.pages[page, 1, :, pos % P, :dv] = v[t].to(cache.pages.dtype)
         return False
 
-    def head_gate(self, o, proj, gate_col0, nh, dv, D, out, ctx):
+    def head_gate(self, o, proj, gate_col0, nh, dv, D, out, ctx, out_col0=0, scale=1.0):
         T = out.shape[0]
         y = o.float().view(T, nh, D)[..., :dv]
         if proj is not None:
             y = y * torch.sigmoid(proj[:, gate_col0:gate_col0 + nh].float())[..., None]
-        y = y * (ctx.row_req[:T] >= 0).float()[:, None, None]
-        out.copy_(y.reshape(T, nh * dv).to(out.dtype))
+        y = y * (ctx.row_req[:T] >= 0).float()[:, None, None] * scale
+        out[:, out_col0:out_col0 + nh * dv] = y.reshape(T, nh * dv).to(out.dtype)
 
     def ssm_scan(self, xbc, proj, dt_col0, dt_bias, a_log, d_skip, state, y, heads, groups, P, N, ctx, writes=True):
         inner = heads * P
@@ -301,14 +301,14 @@ class CpuOps:
             if writes:
                 state[slot] = S
 
-    def head_norm_gate(self, o, weight, eps, gate, gate0, act, out, heads, vdim):
+    def head_norm_gate(self, o, weight, eps, gate, gate0, act, out, heads, vdim, out_col0=0, scale=1.0):
         T = out.shape[0]
         y = o[:T].float().view(T, heads, vdim)
         w = weight.float().view(heads, vdim)[None] if weight.numel() == heads * vdim else weight.float()[None, None, :]
         y = y * torch.rsqrt(y.pow(2).mean(-1, keepdim=True) + eps) * w
         z = gate[:T, gate0:gate0 + heads * vdim].float().view(T, heads, vdim)
         y = y * (z * torch.sigmoid(z) if act == "silu" else torch.sigmoid(z))
-        out.copy_(torch.nan_to_num(y).reshape(T, heads * vdim).to(out.dtype))
+        out[:, out_col0:out_col0 + heads * vdim] = (torch.nan_to_num(y).reshape(T, heads * vdim) * scale).to(out.dtype)
 
     def latent_append(self, proj, c0, rank, weight, eps, ctx, cache):
         table = ctx.block_tables[cache.group]
@@ -530,7 +530,8 @@ class CpuOps:
             n, row0, slot = int(ctx.req_n_rows[r]), int(ctx.req_row_start[r]), int(ctx.req_state_slot[r])
             if n <= 0 or slot < 0:
                 continue
-            S, nn, m = memory[slot].float().clone(), norm_state[slot, :, :d].float().clone(), norm_state[slot, :, d].float().clone()
+            m_at = norm_state.shape[2] - 4                     # copies of n (one per 16 value columns), then m
+            S, nn, m = memory[slot].float().clone(), norm_state[slot, :, :d].float().clone(), norm_state[slot, :, m_at].float().clone()
             for t in range(row0, row0 + n):
                 x = proj[t].float()
                 gi = cap * torch.tanh((x[i0:i0 + H] + bias_i.float()) / cap)
@@ -546,8 +547,8 @@ class CpuOps:
                 out[t] = (torch.einsum("hdv,hd->hv", S, q) / den[:, None]).reshape(H * dv)
             if writes:
                 memory[slot] = S
-                norm_state[slot, :, :d] = nn
-                norm_state[slot, :, d] = m
+                norm_state[slot, :, :m_at] = nn.repeat(1, m_at // d)
+                norm_state[slot, :, m_at] = m
 
     def weighted_sum2(self, a, sa, b, sb, out):
         out.copy_(sa * a + sb * b)

@@ -178,10 +178,12 @@ def _step_ctx(rows_of_reqs, slots, pad_rows=0):
         buf=lambda tag, shape, dt: bufs.setdefault((tag, tuple(shape), dt), torch.empty(shape, dtype=dt, device=DEV)))
 
 
-@pytest.mark.parametrize("H,d,dv", [(2, 8, 12), (3, 40, 50), (1, 4, 4), (4, 64, 64), (2, 128, 32), (1, 200, 24), (2, 6, 7)])
+@pytest.mark.parametrize("H,d,dv", [(2, 8, 12), (3, 40, 50), (1, 4, 4), (4, 64, 64), (2, 128, 32), (1, 200, 24), (2, 6, 7), (16, 128, 512)])
 def test_matrix_memory_walk_from_earlier_states(H, d, dv):
     """Three requests with earlier tokens in their states (one with a large running maximum, one fresh), an idle request
-    slot and two padding rows: results and states after a step of unequal portions, and after the same rows one by one."""
+    slot and two padding rows: results and states after a step of unequal portions, and after the same rows one by one.
+    The last shape has more blocks (3 requests x 16 heads x 32 blocks of columns) than the GPU holds at a time, so blocks
+    of one head run one after another: each must find the head's n as the step before left it."""
     from kungfu_b200 import ops
     g = torch.Generator().manual_seed(H * d + dv)
     rows = [37, 1, 0, 18]
@@ -194,10 +196,12 @@ def test_matrix_memory_walk_from_earlier_states(H, d, dv):
     proj[:, 2 * H * d + H * dv:] *= 3.0                               # gates that reach the cap
     bi, bf = 0.5 * torch.randn(H, generator=g), 3.0 + torch.randn(H, generator=g)
     S0 = torch.randn(4, H, d, dv, generator=g)
-    n0 = torch.zeros(4, H, d + 4)
-    n0[:, :, :d] = torch.randn(4, H, d, generator=g)
-    n0[0, :, d] = 40.0                                                 # a running maximum far from zero
-    n0[2, :, d] = -3.0
+    copies = -(-dv // 16)                                              # a copy of n per 16 value columns, then m
+    m_at = copies * d
+    n0 = torch.zeros(4, H, m_at + 4)
+    n0[:, :, :m_at] = torch.randn(4, H, d, generator=g).repeat(1, 1, copies)
+    n0[0, :, m_at] = 40.0                                              # a running maximum far from zero
+    n0[2, :, m_at] = -3.0
     S0[3], n0[3] = 0.0, 0.0                                            # a fresh request
     q0, k0, v0, i0, f0 = 0, H * d, 2 * H * d, 2 * H * d + H * dv, 2 * H * d + H * dv + H
 
@@ -227,11 +231,14 @@ def test_matrix_memory_walk_from_earlier_states(H, d, dv):
             if n == 0:
                 continue
             sl = slots[r]
-            ref, (Sr, nr, mr) = reference(r, at, n, (S0[sl], n0[sl, :, :d], n0[sl, :, d]))
+            ref, (Sr, nr, mr) = reference(r, at, n, (S0[sl], n0[sl, :, :d], n0[sl, :, m_at]))
             assert _rel(out[at:at + n].view(n, H, dv), ref) < 2e-5, (r, one_by_one)
             # the state in the stabiliser's own units: exp(m) S and exp(m) n are what the design defines
-            got_S = S[sl].double().cpu() * torch.exp(nst[sl, :, d].double().cpu() - mr)[:, None, None]
-            assert _rel(got_S, Sr) < 2e-5 and float((nst[sl, :, d].cpu() - mr).abs().max()) < 1e-3
+            grow = torch.exp(nst[sl, :, m_at].double().cpu() - mr)
+            got_S = S[sl].double().cpu() * grow[:, None, None]
+            assert _rel(got_S, Sr) < 2e-5 and float((nst[sl, :, m_at].cpu() - mr).abs().max()) < 1e-3
+            for c in range(copies):                                    # every block's copy of n
+                assert _rel(nst[sl, :, c * d:(c + 1) * d].double().cpu() * grow[:, None], nr) < 2e-5
             at += n
         assert float(out[T:].abs().max()) == 0.0 and torch.equal(S[1].cpu(), S0[1])          # padding rows, the idle slot
 
