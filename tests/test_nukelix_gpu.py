@@ -232,7 +232,7 @@ def test_matrix_memory_walk_from_earlier_states(H, d, dv):
                 continue
             sl = slots[r]
             ref, (Sr, nr, mr) = reference(r, at, n, (S0[sl], n0[sl, :, :d], n0[sl, :, m_at]))
-            assert _rel(out[at:at + n].view(n, H, dv), ref) < 2e-5, (r, one_by_one)
+            assert _rel(out[at:at + n].view(n, H, dv), ref) < 1e-4, (r, one_by_one)     # 32-bit sums over up to 200 rows of the state
             # the state in the stabiliser's own units: exp(m) S and exp(m) n are what the design defines
             grow = torch.exp(nst[sl, :, m_at].double().cpu() - mr)
             got_S = S[sl].double().cpu() * grow[:, None, None]
